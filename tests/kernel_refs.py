@@ -60,19 +60,156 @@ def gemm_f32_out(a, w):
     return a.to(torch.float32) @ w.to(torch.float32)
 
 
-def embed_rows(table, tokens, out):
-    out.copy_(table[tokens.long()].to(torch.float32))
+def embed_rows(table, tokens, out, scale=1.0):
+    out.copy_(table[tokens.long()].to(torch.float32) * scale)
     return out
 
 
-def add_rmsnorm(residual, delta, scale, eps, out):
+def add_rmsnorm(residual, delta, scale, eps, out, kind="l2_eps"):
     if delta is not None:
         residual += delta.to(torch.float32)
     if out is None:
         return None
     d = residual.shape[-1]
+    if kind == "mean_eps":
+        out.copy_((residual / torch.sqrt(residual.pow(2).mean(-1, keepdim=True) + eps) * scale).to(out.dtype))
+        return out
     norm = residual.pow(2).sum(-1, keepdim=True).sqrt()
     out.copy_((residual * math.sqrt(d) / (norm + eps) * scale).to(out.dtype))
+    return out
+
+
+def glu_clamped(gu, gate_bias, up_bias, limit, alpha, shift, out, hidden):
+    g = gu[:, :hidden].to(torch.float32)
+    u = gu[:, hidden:2 * hidden].to(torch.float32)
+    if gate_bias is not None:
+        g = g + gate_bias
+    if up_bias is not None:
+        u = u + up_bias
+    if limit > 0:
+        g = g.clamp(max=limit)
+        u = u.clamp(min=-limit, max=limit)
+    out[:, :hidden] = (g * torch.sigmoid(alpha * g) * (u + shift)).to(out.dtype)
+    out[:, hidden:] = 0
+    if out.shape[1] > hidden:
+        out[:, hidden] = 1
+    return out
+
+
+def scale_f32(x, scale):
+    x *= scale
+    return x
+
+
+def _segments(row_slot):
+    """[(first row, rows, slot)] of the requests of a step (rows of a request are consecutive)."""
+    segs = []
+    slots = [int(s) for s in row_slot]
+    for r, s in enumerate(slots):
+        if s < 0:
+            continue
+        if segs and segs[-1][2] == s and segs[-1][0] + segs[-1][1] == r:
+            segs[-1] = (segs[-1][0], segs[-1][1] + 1, s)
+        else:
+            segs.append((r, 1, s))
+    return segs
+
+
+def causal_conv(x, weight, state, out, row_slot, row_last, residual=False, silu=False):
+    c, taps = weight.shape
+    hist = taps - 1
+    for r0, rows, slot in _segments(row_slot):
+        assert int(row_last[r0]) == r0 + rows - 1
+        old = state[slot, :hist * c].reshape(hist, c).to(torch.float32)
+        seq = torch.cat([old, x[r0:r0 + rows].to(torch.float32)], dim=0)          # positions -hist .. rows-1
+        y = torch.zeros((rows, c), dtype=torch.float32)
+        for j in range(taps):
+            y += weight[:, j] * seq[j:j + rows]
+        if residual:
+            y += seq[hist:]
+        if silu:
+            y = y * torch.sigmoid(y)
+        out[r0:r0 + rows] = y.to(out.dtype)
+        if hist:
+            state[slot, :hist * c] = seq[rows:].reshape(-1)
+    return out
+
+
+def norm_mix_store(qkv, nq, nk, nv, q_weight, k_weight, eps, v_other, mix, k_pages, v_pages, block_table, positions,
+                   row_slot, page_size, fault):
+    kv_heads = k_pages.shape[1]
+    for r in range(qkv.shape[0]):
+        slot = int(row_slot[r])
+        if slot < 0:
+            continue
+        pos = int(positions[r])
+        row = qkv[r].to(torch.float32)
+        q, k, v = row[:nq], row[nq:nq + nk], row[nq + nk:nq + nk + nv]
+        if q_weight is not None:
+            qkv[r, :nq] = (q / torch.sqrt(q.pow(2).mean() + eps) * q_weight).to(qkv.dtype)
+        if k_weight is not None:
+            k = k / torch.sqrt(k.pow(2).mean() + eps) * k_weight
+        if v_other is not None:
+            lam = float(mix[0])
+            v = (1.0 - lam) * v + lam * v_other[r].to(torch.float32)
+        page = int(block_table[slot, pos // page_size])
+        if page < 0 or page >= k_pages.shape[0]:
+            fault[0] = 3
+            continue
+        k_pages[page, :, pos % page_size, :] = k.view(kv_heads, -1).to(k_pages.dtype)
+        v_pages[page, :, pos % page_size, :] = v.view(kv_heads, -1).to(v_pages.dtype)
+
+
+def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row_slot, num_heads, page_size, window,
+                     scale, bias_slope, bias_rate, fault, step=None):
+    kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
+    g = num_heads // kv_heads
+    for r in range(q.shape[0]):
+        slot = int(row_slot[r])
+        if slot < 0:
+            continue
+        pos = int(positions[r])
+        lo = max(0, pos - window + 1) if window else 0
+        idx = torch.arange(lo, pos + 1)
+        pages = block_table[slot, idx // page_size].long()
+        k = k_pages[pages, :, idx % page_size, :].to(torch.float32).repeat_interleave(g, dim=1)     # (L, H, k_dim)
+        v = v_pages[pages, :, idx % page_size, :].to(torch.float32).repeat_interleave(g, dim=1)
+        qq = q[r].to(torch.float32).view(num_heads, k_dim)
+        s = torch.einsum("hd,khd->hk", qq, k) * scale
+        if bias_slope is not None:
+            s = s - bias_slope[:, None] * torch.log(1.0 + bias_rate[:, None] * (pos - idx).to(torch.float32)[None, :])
+        o = torch.einsum("hk,khd->hd", torch.softmax(s, dim=-1), v).reshape(-1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate[r].to(torch.float32))
+        out[r] = o.to(out.dtype)
+    return out
+
+
+def delta_rule(qkv, beta, decay_in, gate, a_log, dt_bias, norm_weight, eps, unit_eps, q_scale, state, out, row_slot,
+               row_last, num_heads, qk_heads, k_dim, v_dim):
+    H, G = num_heads, qk_heads
+    nq = G * k_dim
+    rate = torch.exp(a_log.to(torch.float32))[:, None]
+    for r0, rows, slot in _segments(row_slot):
+        S = state[slot, :H * k_dim * v_dim].reshape(H, k_dim, v_dim).to(torch.float32).clone()
+        for r in range(r0, r0 + rows):
+            row = qkv[r].to(torch.float32)
+            q = row[:nq].view(G, k_dim)
+            k = row[nq:2 * nq].view(G, k_dim)
+            v = row[2 * nq:2 * nq + H * v_dim].view(H, v_dim)
+            q = (q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * q_scale).repeat_interleave(H // G, dim=0)
+            k = (k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(H // G, dim=0)
+            b = torch.sigmoid(beta[r].to(torch.float32))[:, None]
+            a = decay_in[r].to(torch.float32).view(H, k_dim) + dt_bias.view(H, k_dim)
+            S = torch.exp(-rate * torch.nn.functional.softplus(a))[:, :, None] * S
+            u = b * (v - torch.einsum("hdv,hd->hv", S, k))
+            S = S + k[:, :, None] * u[:, None, :]
+            o = torch.einsum("hdv,hd->hv", S, q)
+            o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_weight
+            if gate is not None:
+                o = o * torch.sigmoid(gate[r].to(torch.float32).view(H, v_dim))
+            out[r] = o.reshape(-1).to(out.dtype)
+        state[slot, :H * k_dim * v_dim] = S.reshape(-1)
     return out
 
 
@@ -317,7 +454,8 @@ def bitmap_set(bitmap_row, tokens):
 
 
 _NAMES = ["rotary_fusable", "gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
-          "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set"]
+          "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set", "glu_clamped", "scale_f32", "causal_conv",
+          "norm_mix_store", "window_attention", "delta_rule"]
 
 
 def install(monkeypatch) -> None:

@@ -204,3 +204,139 @@ def write_config_json(folder: str, cfg: Any) -> None:
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg.to_dict(), f, indent=1)
+
+
+@dataclass
+class KefisunConfig:
+    """Configuration of the Kefisun decoder: pre-norm layers whose mixer is either windowed attention with a
+    logarithmic distance bias or the delta rule with a decay per key channel, every mixer behind a short causal
+    convolution of its input, a clamped gated feed-forward in the layers that have one, tied output matrix.
+
+    ``config.json`` is nested: ``vocab``, ``width``, ``embedding.scale``, ``logit_scale``, ``norm.eps``,
+    ``canon.taps`` (the taps of the convolution in front of every mixer; no ``canon``: none) and ``layers``, a
+    list with, per layer, ``type`` (``attention`` | ``channel_delta``), ``mixer`` (its sizes and constants) and
+    ``mlp`` (``kind``, ``ff``, ``limit``; null: the layer has no feed-forward).  The design has no position
+    table and no context limit of its own: ``max_context`` (optional) bounds what the engine lays out.
+    """
+
+    architecture: ClassVar[str] = "Kefisun"
+    MIXERS: ClassVar[tuple] = ("attention", "channel_delta")
+
+    vocab_size: int
+    hidden_size: int
+    layers: list
+    rms_norm_eps: float = 1e-6
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    canon_taps: Optional[int] = None
+    max_context: int = 1 << 17
+    eos_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        errs = []
+        for name in ("vocab_size", "hidden_size"):
+            v = getattr(self, name)
+            if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                errs.append(f"{name} must be a positive integer, got {v!r}")
+        if not isinstance(self.layers, list) or not self.layers:
+            errs.append("layers must be a non-empty list")
+            raise ConfigError("; ".join(errs))
+        if self.canon_taps is not None and not (isinstance(self.canon_taps, int) and 1 <= self.canon_taps <= 16):
+            errs.append(f"canon.taps must be 1..16, got {self.canon_taps!r}")
+        if not (self.rms_norm_eps >= 0):
+            errs.append(f"norm.eps must be >= 0, got {self.rms_norm_eps}")
+        if self.max_context <= 0:
+            errs.append(f"max_context must be positive, got {self.max_context}")
+        for i, layer in enumerate(self.layers):
+            if not isinstance(layer, dict) or layer.get("type") not in self.MIXERS:
+                errs.append(f"layers[{i}].type must be one of {self.MIXERS}, got "
+                            f"{layer.get('type') if isinstance(layer, dict) else layer!r}")
+                continue
+            m = layer.get("mixer")
+            if not isinstance(m, dict):
+                errs.append(f"layers[{i}].mixer is missing")
+                continue
+            for key in ("heads", "kv_heads", "dim", "vdim"):
+                v = m.get(key)
+                if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                    errs.append(f"layers[{i}].mixer.{key} must be a positive integer, got {v!r}")
+            if isinstance(m.get("heads"), int) and isinstance(m.get("kv_heads"), int) and m["kv_heads"] > 0 \
+                    and m["heads"] % m["kv_heads"]:
+                errs.append(f"layers[{i}].mixer: {m['heads']} heads are not a multiple of {m['kv_heads']} kv heads")
+            conv = m.get("conv")
+            if conv is not None and not (isinstance(conv, int) and 1 <= conv <= 16):
+                errs.append(f"layers[{i}].mixer.conv must be 1..16, got {conv!r}")
+            if layer["type"] == "attention":
+                if not isinstance(m.get("scale"), (int, float)):
+                    errs.append(f"layers[{i}].mixer.scale is missing")
+                mask = m.get("mask")
+                if mask is not None and not (isinstance(mask, dict) and isinstance(mask.get("size"), int)
+                                             and mask["size"] > 0):
+                    errs.append(f"layers[{i}].mixer.mask.size must be a positive integer")
+            elif conv is None:
+                errs.append(f"layers[{i}].mixer.conv is missing")
+            f = layer.get("mlp")
+            if f is not None:
+                if not isinstance(f, dict) or f.get("kind") != "dense":
+                    errs.append(f"layers[{i}].mlp.kind must be 'dense', got {f.get('kind') if isinstance(f, dict) else f!r}")
+                elif not (isinstance(f.get("ff"), int) and f["ff"] > 0):
+                    errs.append(f"layers[{i}].mlp.ff must be a positive integer")
+        if self.torch_dtype not in ("bfloat16", "float32"):
+            errs.append(f"torch_dtype must be bfloat16 or float32, got {self.torch_dtype!r}")
+        if errs:
+            raise ConfigError("; ".join(errs))
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+    def complete_from_shapes(self, shapes: dict) -> None:
+        """Sizes that only the tensors give: the ranks of the two low-rank projections of a ``channel_delta``
+        mixer (``l<i>.mix.a1``, ``l<i>.mix.g1``: (rank, width)), unless the layer's ``mixer`` names them."""
+        for i, layer in enumerate(self.layers):
+            if layer["type"] != "channel_delta":
+                continue
+            for key, tensor in (("decay_rank", f"l{i}.mix.a1"), ("gate_rank", f"l{i}.mix.g1")):
+                if key not in layer["mixer"]:
+                    if tensor not in shapes or len(shapes[tensor]) != 2:
+                        raise ConfigError(f"layers[{i}].mixer.{key} is not given and the weights have no matrix {tensor!r}")
+                    layer["mixer"][key] = int(shapes[tensor][0])
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "KefisunConfig":
+        known = {"architecture", "vocab", "width", "layers", "norm", "embedding", "logit_scale", "canon", "max_context",
+                 "eos_token_id", "torch_dtype"}
+        unknown = sorted(set(raw) - known)
+        missing = [k for k in ("vocab", "width", "layers") if k not in raw]
+        if unknown or missing:
+            parts = []
+            if missing:
+                parts.append("missing keys: " + ", ".join(missing))
+            if unknown:
+                parts.append("unknown keys: " + ", ".join(unknown))
+            raise ConfigError(f"config for architecture {cls.architecture!r}: " + "; ".join(parts))
+        d = dict(vocab_size=raw["vocab"], hidden_size=raw["width"], layers=raw["layers"])
+        if "norm" in raw:
+            d["rms_norm_eps"] = float(raw["norm"]["eps"])
+        if "embedding" in raw:
+            d["embedding_scale"] = float(raw["embedding"].get("scale", 1.0))
+        if "logit_scale" in raw:
+            d["logit_scale"] = float(raw["logit_scale"])
+        if raw.get("canon"):
+            d["canon_taps"] = raw["canon"]["taps"]
+        for k in ("max_context", "eos_token_id", "torch_dtype"):
+            if k in raw:
+                d[k] = raw[k]
+        return cls(**d)
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+             "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale,
+             "norm": {"eps": self.rms_norm_eps}, "layers": self.layers, "max_context": self.max_context,
+             "torch_dtype": self.torch_dtype}
+        if self.canon_taps is not None:
+            d["canon"] = {"taps": self.canon_taps}
+        if self.eos_token_id is not None:
+            d["eos_token_id"] = self.eos_token_id
+        return d

@@ -8,11 +8,11 @@
 #include <cstdlib>
 
 // ----------------------------------------------------------------------------------
-// embedding: residual[r, :] = table[token[r], :]   (the 32-bit residual stream starts here)
+// embedding: residual[r, :] = table[token[r], :] * scale   (the 32-bit residual stream starts here)
 // ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                                  float* __restrict__ out, int d) {
+                                  float* __restrict__ out, int d, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
@@ -24,28 +24,29 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
             float v[N];
             Vec16<T>::load(src + i, v);
 #pragma unroll
-            for (int j = 0; j < N; ++j) dst[i + j] = v[j];
+            for (int j = 0; j < N; ++j) dst[i + j] = v[j] * scale;
         }
     } else {
-        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32(src[i]);
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32(src[i]) * scale;
     }
 }
 
-TIS_API int tis_embed_rows(int dtype, const void* table, const int* tokens, float* out, int n, int d,
+TIS_API int tis_embed_rows(int dtype, const void* table, const int* tokens, float* out, int n, int d, float scale,
                            cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     TIS_DISPATCH_DTYPE(dtype, T,
-        tis_launch(embed_rows_kernel<T>, dim3(n), dim3(256), 0, stream, (const T*)table, tokens, out, d));
+        tis_launch(embed_rows_kernel<T>, dim3(n), dim3(256), 0, stream, (const T*)table, tokens, out, d, scale));
     return tis_check_launch("embed_rows");
 }
 
 // ----------------------------------------------------------------------------------
-// residual += delta ; out = residual * sqrt(d) / (||residual||_2 + eps) * scale
-// (eps is added to the L2 norm itself: main_models_new.py:38-42 of the upstream project)
+// residual += delta ; out = residual * factor(sum of squares) * scale, with the factor of the norm's kind:
+// sqrt(d) / (||residual||_2 + eps) (eps added to the L2 norm itself: main_models_new.py:38-42 of the upstream
+// project) or 1 / sqrt(mean of squares + eps)
 // ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict__ delta,
-                                   const float* __restrict__ scale, float eps, T* __restrict__ out, int d) {
+                                   const float* __restrict__ scale, NormFactor factor, T* __restrict__ out, int d) {
     extern __shared__ float row[];
     __shared__ float red[33];
     pdl_launch_dependents();
@@ -86,7 +87,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
         }
     }
     ss = block_sum(ss, red);
-    const float inv = sqrtf((float)d) / (sqrtf(ss) + eps);
+    const float inv = factor.of(ss);
     if (out == nullptr) return;
     if (vec) {
         for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
@@ -105,7 +106,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
 template <typename T, int CH>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_rows_kernel(float* __restrict__ res, const T* __restrict__ delta, const float* __restrict__ scale,
-                        float eps, T* __restrict__ out, int n, int d) {
+                        NormFactor factor, T* __restrict__ out, int n, int d) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int N = Vec16<T>::N;
@@ -139,7 +140,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ res, const T* __restrict__ delta, co
     }
     if (out == nullptr) return;
     ss = warp_sum(ss);
-    const float inv = sqrtf((float)d) / (sqrtf(ss) + eps);
+    const float inv = factor.of(ss);
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
         const int i = (lane + 32 * k) * N;
@@ -157,7 +158,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ res, const T* __restrict__ delta, co
 }
 
 template <typename T, int CH>
-static void launch_add_rmsnorm_rows(float* residual, const T* delta, const float* scale, float eps, T* out, int n,
+static void launch_add_rmsnorm_rows(float* residual, const T* delta, const float* scale, NormFactor eps, T* out, int n,
                                     int d, cudaStream_t stream) {
     const int threads = 128;          // four rows a CTA (measured at 2048 x 1536: 9.0 us; eight rows 10.0 us)
     const int rows = threads / 32;
@@ -165,9 +166,14 @@ static void launch_add_rmsnorm_rows(float* residual, const T* delta, const float
                eps, out, n, d);
 }
 
-TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const float* scale, float eps,
-                            void* out, int n, int d, cudaStream_t stream) {
+TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const float* scale, float eps_value,
+                            int kind, void* out, int n, int d, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
+    if (kind < TIS_NORM_L2_EPS || kind > TIS_NORM_MEAN_EPS) {
+        tis_set_error("add_rmsnorm: norm kind %d", kind);
+        return TIS_BAD_SIZE;
+    }
+    const NormFactor eps = norm_factor(kind, d, eps_value);
     if ((size_t)d * sizeof(float) > 96 * 1024) {
         tis_set_error("add_rmsnorm: width %d too large (one row must fit 96 KB of shared memory)", d);
         return TIS_BAD_SIZE;
@@ -499,6 +505,73 @@ TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, int b
         tis_launch(swiglu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, F, block,
                    total));
     return tis_check_launch("swiglu");
+}
+
+// ----------------------------------------------------------------------------------
+// Gated linear unit with biases and clamps.  A row of `gu` holds F gate columns, then F up columns:
+//   g = min(gate + bg, limit), u = clamp(up + bu, -limit, limit), out = g * sigmoid(alpha * g) * (u + shift).
+// `limit` <= 0: no clamps.  The columns F..ldo-1 of `out` get 1, 0, 0, ...: with the bias of the product that
+// follows as one more row of its matrix, that product adds the bias itself.
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, int ldg, const float* __restrict__ bg,
+                                   const float* __restrict__ bu, float limit, float alpha, float shift,
+                                   T* __restrict__ out, int ldo, int F, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / ldo;
+        const int j = (int)(idx - r * ldo);
+        float y;
+        if (j < F) {
+            float g = to_f32(gu[r * ldg + j]) + (bg != nullptr ? bg[j] : 0.f);
+            float u = to_f32(gu[r * ldg + F + j]) + (bu != nullptr ? bu[j] : 0.f);
+            if (limit > 0.f) {
+                g = fminf(g, limit);
+                u = fminf(fmaxf(u, -limit), limit);
+            }
+            y = g / (1.f + expf(-alpha * g)) * (u + shift);
+        } else {
+            y = j == F ? 1.f : 0.f;
+        }
+        out[idx] = from_f32<T>(y);
+    }
+}
+
+TIS_API int tis_glu_clamped(int dtype, const void* gu, int ldg, const float* bg, const float* bu, float limit,
+                            float alpha, float shift, void* out, int ldo, int n, int F, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (F <= 0 || ldo < F || ldg < 2 * F) {
+        tis_set_error("glu_clamped: %d columns, row lengths %d in and %d out", F, ldg, ldo);
+        return TIS_BAD_SIZE;
+    }
+    const size_t total = (size_t)n * ldo;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(glu_clamped_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)gu, ldg, bg, bu, limit,
+                   alpha, shift, (T*)out, ldo, F, total));
+    return tis_check_launch("glu_clamped");
+}
+
+// ----------------------------------------------------------------------------------
+// x *= scale over `total` floats (the logits of a model that scales them)
+// ----------------------------------------------------------------------------------
+__global__ void scale_f32_kernel(float* __restrict__ x, float scale, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] *= scale;
+}
+
+TIS_API int tis_scale_f32(float* x, float scale, size_t total, cudaStream_t stream) {
+    if (total == 0) return TIS_OK;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    tis_launch(scale_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, scale, total);
+    return tis_check_launch("scale_f32");
 }
 
 // ----------------------------------------------------------------------------------

@@ -1,0 +1,523 @@
+// Kernels of mixers that are not plain rotary attention:
+//   * a short causal convolution over time on each channel, with the last inputs of a request kept in its state;
+//   * the step between the projections and the cache of an attention whose queries and keys are normalised as a
+//     whole and whose values are mixed with another layer's: norm, mix, write into the pages;
+//   * attention over a window of the paged cache with keys and values of different widths, a bias on the scores
+//     that grows with the logarithm of the distance, and a sigmoid gate on the output;
+//   * the delta rule with a decay per head and key channel, a recurrence over a matrix state per head.
+// Everything is computed in 32-bit; T is the storage type of activations and pages.
+//
+// Rows of a step: row r belongs to request slot row_slot[r] (negative: padding) at positions[r]; the rows of a
+// request are consecutive and in order, row_last[r] is the last row of r's request in this step.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------------------------
+// y[r, c] = (residual ? x[r, c] : 0) + sum_j w[c, j] * x(t - taps + 1 + j)[c], optionally through silu.
+// x(t') of a position before this step's rows of the request comes from the request's state, which holds its
+// last taps-1 inputs (oldest first, zero before the start of the sequence) and is brought up to date here.
+//
+// A thread owns one (row, channel).  The state of a (request, channel) is read and written by one thread only:
+// the thread of the request's first row in this step computes the first taps-1 rows of the request, which are the
+// ones that need the state, and then writes the new state; the threads of those rows do nothing.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int CONV_MAX_TAPS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ state,
+                   size_t state_stride, T* __restrict__ out, int ldo, const int* __restrict__ row_slot,
+                   const int* __restrict__ row_last, int n, int C, int taps, int residual, int act_silu) {
+    pdl_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (c >= C) return;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int hist = taps - 1;
+    int back = 0;
+    while (back < hist && r - back - 1 >= 0 && row_slot[r - back - 1] == slot) ++back;
+    if (back > 0 && back < hist) return;              // computed by the thread of the request's first row
+    float wt[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+    pdl_wait();
+    if (back == hist) {                               // every input is a row of this step (or there is no history)
+        float acc = 0.f, cur = 0.f;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < taps) {
+                cur = to_f32(x[(size_t)(r - hist + j) * ldx + c]);
+                acc = fmaf(wt[j], cur, acc);
+            }
+        }
+        if (residual) acc += cur;
+        if (act_silu) acc = acc / (1.f + expf(-acc));
+        out[(size_t)r * ldo + c] = from_f32<T>(acc);
+        return;
+    }
+    // the first row of a request in this step
+    const int rows = row_last[r] - r + 1;
+    float* st = state + (size_t)slot * state_stride;
+    float h[CONV_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; ++k) h[k] = k < hist ? st[(size_t)k * C + c] : 0.f;
+    const int mine = rows < hist ? rows : hist;
+    for (int i = 0; i < mine; ++i) {
+        const float cur = to_f32(x[(size_t)(r + i) * ldx + c]);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < CONV_MAX_TAPS; ++k)
+            if (k < hist) acc = fmaf(wt[k], h[k], acc);
+        acc = fmaf(wt[hist], cur, acc);
+        if (residual) acc += cur;
+        if (act_silu) acc = acc / (1.f + expf(-acc));
+        out[(size_t)(r + i) * ldo + c] = from_f32<T>(acc);
+#pragma unroll
+        for (int k = 0; k + 1 < CONV_MAX_TAPS; ++k)
+            if (k + 1 < hist) h[k] = h[k + 1];
+#pragma unroll
+        for (int k = 0; k < CONV_MAX_TAPS; ++k)
+            if (k == hist - 1) h[k] = cur;
+    }
+    if (rows > hist) {
+#pragma unroll
+        for (int k = 0; k < CONV_MAX_TAPS; ++k)
+            if (k < hist) h[k] = to_f32(x[(size_t)(r + rows - hist + k) * ldx + c]);
+    }
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; ++k)
+        if (k < hist) st[(size_t)k * C + c] = h[k];
+}
+
+TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, float* state, size_t state_stride,
+                            void* out, int ldo, const int* row_slot, const int* row_last, int n, int C, int taps,
+                            int residual, int act_silu, cudaStream_t stream) {
+    if (n <= 0 || C <= 0) return TIS_OK;
+    if (taps < 1 || taps > CONV_MAX_TAPS) {
+        tis_set_error("causal_conv: %d taps; this kernel takes 1..%d", taps, CONV_MAX_TAPS);
+        return TIS_BAD_SIZE;
+    }
+    if (x == out) {
+        tis_set_error("causal_conv: a row reads the rows before it, so the result needs a place of its own");
+        return TIS_BAD_SIZE;
+    }
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(causal_conv_kernel<T>, dim3((C + 127) / 128, n), dim3(128), 0, stream, (const T*)x, ldx, w, state,
+                   state_stride, (T*)out, ldo, row_slot, row_last, n, C, taps, residual, act_silu));
+    return tis_check_launch("causal_conv");
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Between the projections and the cache.  A row of `qkv` holds nq query, nk key and nv value elements (all heads).
+//   queries: q * rsqrt(mean(q^2) + eps) * wq over all nq elements at once, in place (wq null: left as they are);
+//   keys: the same with wk over nk elements, written into the row's page;
+//   values: (1 - lambda) * v + lambda * v_other (v_other null: v itself), written into the row's page.
+// Pages: element (page, kv head, position in the page, i) of the keys at k_pages + page * k_page_stride +
+// head * k_head_stride + position * k_dim + i; the values likewise.
+// ------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_mix_store_kernel(T* __restrict__ qkv, int ld, int nq, int nk, int nv, const float* __restrict__ wq,
+                      const float* __restrict__ wk, float eps, const T* __restrict__ v_other, int ld_other,
+                      const float* __restrict__ lambda, T* __restrict__ k_pages, size_t k_page_stride,
+                      size_t k_head_stride, T* __restrict__ v_pages, size_t v_page_stride, size_t v_head_stride,
+                      int kv_heads, int page_size, int num_pages, const int* __restrict__ block_table, int bt_stride,
+                      const int* __restrict__ positions, const int* __restrict__ row_slot, int* __restrict__ fault) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = positions[r];
+    const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
+    pdl_wait();
+    T* row = qkv + (size_t)r * ld;
+    float sq = 0.f, sk = 0.f;
+    if (wq != nullptr)
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = to_f32(row[i]); sq += v * v; }
+    if (wk != nullptr)
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = to_f32(row[nq + i]); sk += v * v; }
+    if (wq != nullptr) {
+        sq = block_sum(sq, red);
+        const float f = rsqrtf(sq / (float)nq + eps);
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) row[i] = from_f32<T>(to_f32(row[i]) * f * wq[i]);
+    }
+    float fk = 1.f;
+    if (wk != nullptr) {
+        sk = block_sum(sk, red);
+        fk = rsqrtf(sk / (float)nk + eps);
+    }
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicExch(fault, 3);
+        return;
+    }
+    const int in_page = pos % page_size;
+    const int k_dim = nk / kv_heads, v_dim = nv / kv_heads;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int head = i / k_dim, e = i - head * k_dim;
+        const float v = to_f32(row[nq + i]) * fk * (wk != nullptr ? wk[i] : 1.f);
+        k_pages[(size_t)page * k_page_stride + (size_t)head * k_head_stride + (size_t)in_page * k_dim + e] = from_f32<T>(v);
+    }
+    const float lam = (v_other != nullptr && lambda != nullptr) ? lambda[0] : 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const int head = i / v_dim, e = i - head * v_dim;
+        float v = to_f32(row[nq + nk + i]);
+        if (v_other != nullptr) v = (1.f - lam) * v + lam * to_f32(v_other[(size_t)r * ld_other + i]);
+        v_pages[(size_t)page * v_page_stride + (size_t)head * v_head_stride + (size_t)in_page * v_dim + e] = from_f32<T>(v);
+    }
+}
+
+TIS_API int tis_norm_mix_store(int dtype, void* qkv, int ld, int nq, int nk, int nv, const float* wq, const float* wk,
+                               float eps, const void* v_other, int ld_other, const float* lambda, void* k_pages,
+                               size_t k_page_stride, size_t k_head_stride, void* v_pages, size_t v_page_stride,
+                               size_t v_head_stride, int kv_heads, int page_size, int num_pages,
+                               const int* block_table, int bt_stride, const int* positions, const int* row_slot,
+                               int* fault, int n, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (kv_heads <= 0 || nk % kv_heads || nv % kv_heads || page_size <= 0) {
+        tis_set_error("norm_mix_store: %d key and %d value elements for %d kv heads, page size %d", nk, nv, kv_heads,
+                      page_size);
+        return TIS_BAD_SIZE;
+    }
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(norm_mix_store_kernel<T>, dim3(n), dim3(256), 0, stream, (T*)qkv, ld, nq, nk, nv, wq, wk, eps,
+                   (const T*)v_other, ld_other, lambda, (T*)k_pages, k_page_stride, k_head_stride, (T*)v_pages,
+                   v_page_stride, v_head_stride, kv_heads, page_size, num_pages, block_table, bt_stride, positions,
+                   row_slot, fault));
+    return tis_check_launch("norm_mix_store");
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Attention of one row and query head over the keys lo..pos of its request's pages, lo = max(0, pos - window + 1)
+// (window 0: lo = 0):  score_j = q . k_j * scale - r1[head] * ln(1 + r2[head] * (pos - j)), softmax, times values,
+// times sigmoid(gate) element by element.  r1 null: no bias; gate null: no gate.
+// A CTA of 128 threads: 128 keys a tile, a thread a key for the scores; for the values the threads form
+// 128 / v_dim groups, each taking every groups-th key of the tile, a thread a value column.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int WA_THREADS = 128;
+constexpr int WA_MAX_COLS = 4;          // value columns a thread keeps: v_dim <= 512
+
+template <typename T>
+__global__ void __launch_bounds__(WA_THREADS)
+window_attention_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ gate, int ldg, T* __restrict__ out,
+                        int ldo, const T* __restrict__ k_pages, size_t k_page_stride, size_t k_head_stride,
+                        const T* __restrict__ v_pages, size_t v_page_stride, size_t v_head_stride,
+                        const int* __restrict__ block_table, int bt_stride, int num_pages,
+                        const int* __restrict__ positions, const int* __restrict__ row_slot, int H, int G, int k_dim,
+                        int v_dim, int page_size, int window, float scale, const float* __restrict__ r1,
+                        const float* __restrict__ r2, int* __restrict__ fault) {
+    extern __shared__ float smem[];
+    __shared__ float red[33];
+    __shared__ int page_of[WA_THREADS];
+    pdl_launch_dependents();
+    const int r = blockIdx.x, head = blockIdx.y;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = positions[r];
+    const int kvh = head / (H / G);
+    const float b1 = r1 != nullptr ? r1[head] : 0.f, b2 = r1 != nullptr ? r2[head] : 0.f;
+    float* qs = smem;                                   // [k_dim]
+    float* ps = qs + k_dim;                             // [WA_THREADS]
+    float* part = ps + WA_THREADS;                      // [groups][v_dim]
+    const int tid = threadIdx.x;
+    pdl_wait();
+    for (int i = tid; i < k_dim; i += WA_THREADS) qs[i] = to_f32(q[(size_t)r * ldq + (size_t)head * k_dim + i]);
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int hi = pos + 1;
+    // value columns
+    const int groups = v_dim >= WA_THREADS ? 1 : WA_THREADS / v_dim;
+    const int grp = v_dim >= WA_THREADS ? 0 : tid / v_dim;
+    const int col0 = v_dim >= WA_THREADS ? tid : tid - grp * v_dim;
+    const bool works = grp < groups;
+    float acc[WA_MAX_COLS];
+#pragma unroll
+    for (int a = 0; a < WA_MAX_COLS; ++a) acc[a] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    __syncthreads();
+    for (int base = lo; base < hi; base += WA_THREADS) {
+        const int j = base + tid;
+        float s = -INFINITY;
+        int page = -1;
+        if (j < hi) {
+            page = block_table[(size_t)slot * bt_stride + j / page_size];
+            if (page < 0 || page >= num_pages) {
+                atomicExch(fault, 4);
+                page = -1;
+            } else {
+                const T* kr = k_pages + (size_t)page * k_page_stride + (size_t)kvh * k_head_stride +
+                              (size_t)(j % page_size) * k_dim;
+                float d = 0.f;
+                for (int i = 0; i < k_dim; ++i) d = fmaf(qs[i], to_f32(kr[i]), d);
+                s = d * scale - b1 * logf(1.f + b2 * (float)(pos - j));
+            }
+        }
+        page_of[tid] = page;
+        const float m_new = fmaxf(m, block_max(s, red));
+        const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+        const float p = (s == -INFINITY || m_new == -INFINITY) ? 0.f : expf(s - m_new);
+        l = l * corr + block_sum(p, red);
+        m = m_new;
+        ps[tid] = p;
+#pragma unroll
+        for (int a = 0; a < WA_MAX_COLS; ++a) acc[a] *= corr;
+        __syncthreads();
+        if (works) {
+            const int cnt = min(WA_THREADS, hi - base);
+            for (int t = grp; t < cnt; t += groups) {
+                const int pg = page_of[t];
+                if (pg < 0) continue;
+                const float pt = ps[t];
+                const T* vr = v_pages + (size_t)pg * v_page_stride + (size_t)kvh * v_head_stride +
+                              (size_t)((base + t) % page_size) * v_dim;
+#pragma unroll
+                for (int a = 0; a < WA_MAX_COLS; ++a) {
+                    const int c = col0 + a * WA_THREADS;
+                    if (c < v_dim) acc[a] = fmaf(pt, to_f32(vr[c]), acc[a]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (groups > 1) {
+        if (works) part[grp * v_dim + col0] = acc[0];
+        __syncthreads();
+        if (tid < v_dim) {
+            float s = 0.f;
+            for (int g2 = 0; g2 < groups; ++g2) s += part[g2 * v_dim + tid];
+            acc[0] = s;
+        }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (grp == 0) {
+#pragma unroll
+        for (int a = 0; a < WA_MAX_COLS; ++a) {
+            const int c = col0 + a * WA_THREADS;
+            if (c < v_dim) {
+                float o = acc[a] * inv;
+                if (gate != nullptr) {
+                    const float gv = to_f32(gate[(size_t)r * ldg + (size_t)head * v_dim + c]);
+                    o = o / (1.f + expf(-gv));
+                }
+                out[(size_t)r * ldo + (size_t)head * v_dim + c] = from_f32<T>(o);
+            }
+        }
+    }
+}
+
+TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* gate, int ldg, void* out, int ldo,
+                                 const void* k_pages, size_t k_page_stride, size_t k_head_stride, const void* v_pages,
+                                 size_t v_page_stride, size_t v_head_stride, const int* block_table, int bt_stride,
+                                 int num_pages, const int* positions, const int* row_slot, int n, int H, int G,
+                                 int k_dim, int v_dim, int page_size, int window, float scale, const float* r1,
+                                 const float* r2, int* fault, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > WA_THREADS * WA_MAX_COLS || page_size <= 0 ||
+        window < 0) {
+        tis_set_error("window_attention: %d query heads, %d kv heads, key width %d, value width %d (at most %d), "
+                      "page size %d, window %d", H, G, k_dim, v_dim, WA_THREADS * WA_MAX_COLS, page_size, window);
+        return TIS_BAD_SIZE;
+    }
+    const int groups = v_dim >= WA_THREADS ? 1 : WA_THREADS / v_dim;
+    const size_t smem = sizeof(float) * ((size_t)k_dim + WA_THREADS + (size_t)groups * v_dim);
+    TIS_DISPATCH_DTYPE(dtype, T,
+        tis_launch(window_attention_kernel<T>, dim3(n, H), dim3(WA_THREADS), smem, stream, (const T*)q, ldq,
+                   (const T*)gate, ldg, (T*)out, ldo, (const T*)k_pages, k_page_stride, k_head_stride, (const T*)v_pages,
+                   v_page_stride, v_head_stride, block_table, bt_stride, num_pages, positions, row_slot, H, G, k_dim,
+                   v_dim, page_size, window, scale, r1, r2, fault));
+    return tis_check_launch("window_attention");
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// The delta rule with a decay per head and key channel.  Per request and head a state S (k_dim x v_dim, 32-bit):
+//   q^ = q / sqrt(sum q^2 + unit_eps) * q_scale,  k^ = k / sqrt(sum k^2 + unit_eps)          (per head)
+//   beta = sigmoid(b),  g_i = exp(-exp(A_log[head]) * softplus(a_i + dt_bias_i))               (per key channel i)
+//   S <- diag(g) S;  u = beta * (v - S^T k^);  S <- S + k^ u^T;  o = S^T q^
+//   out = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate)                                   (over v_dim)
+// A row of `qkv` holds the queries and keys of G heads (k_dim each) and the values of H heads (v_dim each).
+// One CTA per (request of the step, head); the CTAs of rows that are not the first of their request leave at once.
+// Every column of S is a recurrence of its own: a thread keeps one column (in registers when DIM > 0 is the key
+// width, else in shared memory).  Tokens are taken CHUNK at a time: all threads prepare q^, k^, g, beta and v of
+// the chunk, then every thread walks its column through the chunk without a barrier, then the outputs of the
+// chunk are normalised, a warp a token.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int DELTA_CHUNK = 16;
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+template <typename T, int DIM>
+__global__ void __launch_bounds__(256)
+delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
+                  int lda, const T* __restrict__ gate, int ldg, const float* __restrict__ A_log,
+                  const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps, float unit_eps,
+                  float q_scale, float* __restrict__ state, size_t state_stride, T* __restrict__ out, int ldo,
+                  const int* __restrict__ row_slot, const int* __restrict__ row_last, int H, int G, int k_dim_rt,
+                  int v_dim) {
+    extern __shared__ float smem[];
+    pdl_launch_dependents();
+    const int r0 = blockIdx.x, head = blockIdx.y;
+    const int slot = row_slot[r0];
+    if (slot < 0) return;
+    if (r0 > 0 && row_slot[r0 - 1] == slot) return;
+    const int k_dim = DIM > 0 ? DIM : k_dim_rt;
+    const int rows = row_last[r0] - r0 + 1;
+    const int kvh = head / (H / G);
+    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+    float* qs = smem;                                   // [CHUNK][k_dim]
+    float* ks = qs + DELTA_CHUNK * k_dim;
+    float* gs = ks + DELTA_CHUNK * k_dim;
+    float* vs = gs + DELTA_CHUNK * k_dim;               // [CHUNK][v_dim]
+    float* os = vs + DELTA_CHUNK * v_dim;               // [CHUNK][v_dim]
+    float* betas = os + DELTA_CHUNK * v_dim;            // [CHUNK]
+    float* S_sh = betas + DELTA_CHUNK;                  // [k_dim][v_dim] when DIM == 0
+    const float decay_rate = expf(A_log[head]);
+    float* S_glob = state + (size_t)slot * state_stride + (size_t)head * k_dim * v_dim;
+    constexpr int REG = DIM > 0 ? DIM : 1;
+    float S[REG];
+    pdl_wait();
+    if (tid < v_dim) {
+        if (DIM > 0) {
+#pragma unroll
+            for (int i = 0; i < REG; ++i) S[i] = S_glob[(size_t)i * v_dim + tid];
+        } else {
+            for (int i = 0; i < k_dim; ++i) S_sh[i * v_dim + tid] = S_glob[(size_t)i * v_dim + tid];
+        }
+    }
+    const int q_off = kvh * k_dim, k_off = G * k_dim + kvh * k_dim, v_off = 2 * G * k_dim + head * v_dim;
+    for (int c0 = 0; c0 < rows; c0 += DELTA_CHUNK) {
+        const int cnt = min(DELTA_CHUNK, rows - c0);
+        __syncthreads();                                // the chunk before is done with the shared arrays
+        for (int t = warp; t < cnt; t += nwarps) {
+            const T* row = qkv + (size_t)(r0 + c0 + t) * ld;
+            float sq = 0.f, sk = 0.f;
+            for (int i = lane; i < k_dim; i += 32) {
+                const float qv = to_f32(row[q_off + i]), kv = to_f32(row[k_off + i]);
+                sq += qv * qv;
+                sk += kv * kv;
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.f / sqrtf(sk + unit_eps);
+            for (int i = lane; i < k_dim; i += 32) {
+                qs[t * k_dim + i] = to_f32(row[q_off + i]) * fq;
+                ks[t * k_dim + i] = to_f32(row[k_off + i]) * fk;
+                const float a = to_f32(a_in[(size_t)(r0 + c0 + t) * lda + head * k_dim + i]) + dt_bias[head * k_dim + i];
+                gs[t * k_dim + i] = expf(-decay_rate * softplus_f(a));
+            }
+            for (int j = lane; j < v_dim; j += 32) vs[t * v_dim + j] = to_f32(row[v_off + j]);
+            if (lane == 0) {
+                const float bv = to_f32(b_in[(size_t)(r0 + c0 + t) * ldb + head]);
+                betas[t] = 1.f / (1.f + expf(-bv));
+            }
+        }
+        __syncthreads();
+        if (tid < v_dim) {
+            for (int t = 0; t < cnt; ++t) {
+                const float* kt = ks + t * k_dim;
+                const float* qt = qs + t * k_dim;
+                const float* gt = gs + t * k_dim;
+                float dot = 0.f, o = 0.f;
+                if (DIM > 0) {
+#pragma unroll
+                    for (int i = 0; i < REG; ++i) {
+                        S[i] *= gt[i];
+                        dot = fmaf(S[i], kt[i], dot);
+                    }
+                    const float u = betas[t] * (vs[t * v_dim + tid] - dot);
+#pragma unroll
+                    for (int i = 0; i < REG; ++i) {
+                        S[i] = fmaf(kt[i], u, S[i]);
+                        o = fmaf(S[i], qt[i], o);
+                    }
+                } else {
+                    for (int i = 0; i < k_dim; ++i) {
+                        const float s = S_sh[i * v_dim + tid] * gt[i];
+                        S_sh[i * v_dim + tid] = s;
+                        dot = fmaf(s, kt[i], dot);
+                    }
+                    const float u = betas[t] * (vs[t * v_dim + tid] - dot);
+                    for (int i = 0; i < k_dim; ++i) {
+                        const float s = fmaf(kt[i], u, S_sh[i * v_dim + tid]);
+                        S_sh[i * v_dim + tid] = s;
+                        o = fmaf(s, qt[i], o);
+                    }
+                }
+                os[t * v_dim + tid] = o;
+            }
+        }
+        __syncthreads();
+        for (int t = warp; t < cnt; t += nwarps) {
+            float ss = 0.f;
+            for (int j = lane; j < v_dim; j += 32) { const float o = os[t * v_dim + j]; ss += o * o; }
+            ss = warp_sum(ss);
+            const float f = rsqrtf(ss / (float)v_dim + eps);
+            const size_t rr = (size_t)(r0 + c0 + t);
+            for (int j = lane; j < v_dim; j += 32) {
+                float o = os[t * v_dim + j] * f * norm_w[j];
+                if (gate != nullptr) {
+                    const float gv = to_f32(gate[rr * ldg + head * v_dim + j]);
+                    o = o / (1.f + expf(-gv));
+                }
+                out[rr * ldo + head * v_dim + j] = from_f32<T>(o);
+            }
+        }
+    }
+    if (tid < v_dim) {
+        if (DIM > 0) {
+#pragma unroll
+            for (int i = 0; i < REG; ++i) S_glob[(size_t)i * v_dim + tid] = S[i];
+        } else {
+            for (int i = 0; i < k_dim; ++i) S_glob[(size_t)i * v_dim + tid] = S_sh[i * v_dim + tid];
+        }
+    }
+}
+
+template <typename T, int DIM>
+static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const T* a_in, int lda, const T* gate, int ldg,
+                             const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
+                             float q_scale, float* state, size_t state_stride, T* out, int ldo, const int* row_slot,
+                             const int* row_last, int n, int H, int G, int k_dim, int v_dim, cudaStream_t stream) {
+    int threads = (v_dim + 31) / 32 * 32;
+    if (threads < 128) threads = 128;                  // warps to prepare and normalise a chunk with
+    size_t smem = sizeof(float) * ((size_t)DELTA_CHUNK * (3 * k_dim + 2 * v_dim + 1) + (DIM > 0 ? 0 : (size_t)k_dim * v_dim));
+    if (smem > 200 * 1024) {
+        tis_set_error("delta_rule: key width %d x value width %d does not fit shared memory", k_dim, v_dim);
+        return TIS_BAD_SIZE;
+    }
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(delta_rule_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    tis_launch(delta_rule_kernel<T, DIM>, dim3(n, H), dim3(threads), smem, stream, qkv, ld, b_in, ldb, a_in, lda, gate, ldg,
+               A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, out, ldo, row_slot, row_last, H, G,
+               k_dim, v_dim);
+    return tis_check_launch("delta_rule");
+}
+
+TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in, int ldb, const void* a_in, int lda,
+                           const void* gate, int ldg, const float* A_log, const float* dt_bias, const float* norm_w,
+                           float eps, float unit_eps, float q_scale, float* state, size_t state_stride, void* out,
+                           int ldo, const int* row_slot, const int* row_last, int n, int H, int G, int k_dim, int v_dim,
+                           cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > 256) {
+        tis_set_error("delta_rule: %d heads, %d query/key heads, key width %d, value width %d (at most 256)", H, G, k_dim,
+                      v_dim);
+        return TIS_BAD_SIZE;
+    }
+#define TIS_DELTA_CASE(D)                                                                                              \
+    case D:                                                                                                            \
+        TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule<T, D>((const T*)qkv, ld, (const T*)b_in, ldb,            \
+            (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state,           \
+            state_stride, (T*)out, ldo, row_slot, row_last, n, H, G, k_dim, v_dim, stream));                           \
+        break;
+    switch (k_dim) {
+        TIS_DELTA_CASE(16)
+        TIS_DELTA_CASE(32)
+        TIS_DELTA_CASE(64)
+        TIS_DELTA_CASE(128)
+        default: break;
+    }
+#undef TIS_DELTA_CASE
+    TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule<T, 0>((const T*)qkv, ld, (const T*)b_in, ldb, (const T*)a_in,
+        lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, (T*)out, ldo,
+        row_slot, row_last, n, H, G, k_dim, v_dim, stream));
+    return TIS_OK;
+}

@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 4
+ABI_VERSION = 5
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -506,21 +506,23 @@ def gemm_f32_out(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 # row-wise kernels
 # ---------------------------------------------------------------------------------------
 
-def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[r] = float(table[tokens[r]]); out is the float32 residual stream (n, d)."""
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[r] = float(table[tokens[r]]) * scale; out is the float32 residual stream (n, d)."""
     lib = library()
     n, d = out.shape
-    _check(lib.tis_embed_rows(_dt(table), _p(table), _p(tokens), _p(out), n, d, _stream()), lib)
+    _check(lib.tis_embed_rows(_dt(table), _p(table), _p(tokens), _p(out), n, d, _f(scale), _stream()), lib)
     return out
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], scale: torch.Tensor, eps: float,
-                out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    """residual += delta (when given), then out = residual*sqrt(d)/(||residual||+eps)*scale."""
+                out: Optional[torch.Tensor], kind: str = "l2_eps") -> Optional[torch.Tensor]:
+    """residual += delta (when given), then out = residual * factor * scale with the row's factor of ``kind``
+    (``NORM_KINDS``): sqrt(d) / (||residual|| + eps), or 1 / sqrt(mean(residual^2) + eps)."""
     lib = library()
     n, d = residual.shape
     ref = out if out is not None else delta
-    _check(lib.tis_add_rmsnorm(_dt(ref), _p(residual), _p(delta), _p(scale), _f(eps), _p(out), n, d, _stream()), lib)
+    _check(lib.tis_add_rmsnorm(_dt(ref), _p(residual), _p(delta), _p(scale), _f(eps), NORM_KINDS[kind], _p(out), n, d,
+                               _stream()), lib)
     return out
 
 
@@ -759,6 +761,111 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, block: Optional[int] = None) -> 
     lib = library()
     n, f = out.shape
     _check(lib.tis_swiglu(_dt(gu), _p(gu), _p(out), n, f, block or f, _stream()), lib)
+    return out
+
+
+def glu_clamped(gu: torch.Tensor, gate_bias: Optional[torch.Tensor], up_bias: Optional[torch.Tensor], limit: float,
+                alpha: float, shift: float, out: torch.Tensor, hidden: int) -> torch.Tensor:
+    """A row of ``gu`` holds ``hidden`` gate columns, then as many up columns.  g = min(gate + bias, limit),
+    u = clamp(up + bias, -limit, limit) (``limit`` <= 0: unclamped); out[:, :hidden] = g * sigmoid(alpha * g) *
+    (u + shift); the columns of ``out`` beyond ``hidden`` get 1, 0, 0, ... (a column of ones for the bias of the
+    product that follows)."""
+    lib = library()
+    n = gu.shape[0]
+    _check(lib.tis_glu_clamped(_dt(gu), _p(gu), gu.stride(0), _p(gate_bias), _p(up_bias), _f(limit), _f(alpha), _f(shift),
+                               _p(out), out.stride(0), n, hidden, _stream()), lib)
+    return out
+
+
+def scale_f32(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x *= scale in place (contiguous float32)."""
+    lib = library()
+    _check(lib.tis_scale_f32(_p(x), _f(scale), ctypes.c_size_t(x.numel()), _stream()), lib)
+    return x
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
+                row_last: torch.Tensor, residual: bool = False, silu: bool = False) -> torch.Tensor:
+    """A causal convolution over time on each channel: ``out[r, c] = (x[r, c] if residual) + sum_j weight[c, j] *
+    x(t - taps + 1 + j)[c]``, through silu if asked.  ``x`` (n, C) with a free row stride; ``weight`` (C, taps)
+    float32; ``state`` (slots, taps - 1, C) float32 (a view with a free slot stride): the last inputs of every
+    request, oldest first, zero before the start of a sequence; read for the rows whose history lies before this
+    step and brought up to date."""
+    lib = library()
+    n, c = x.shape
+    taps = weight.shape[1]
+    _check(lib.tis_causal_conv(_dt(x), _p(x), x.stride(0), _p(weight), _p(state), ctypes.c_size_t(state.stride(0)),
+                               _p(out), out.stride(0), _p(row_slot), _p(row_last), n, c, taps, int(residual), int(silu),
+                               _stream()), lib)
+    return out
+
+
+def _page_strides(pages: torch.Tensor, width: int):
+    """(page stride, head stride) of a view [pages, kv_heads, page_size, width] whose rows are dense."""
+    if pages.stride(3) != 1 or pages.stride(2) != width:
+        raise KernelError("cache pages: the rows of a kv head must lie one after the other")
+    return ctypes.c_size_t(pages.stride(0)), ctypes.c_size_t(pages.stride(1))
+
+
+def norm_mix_store(qkv: torch.Tensor, nq: int, nk: int, nv: int, q_weight: Optional[torch.Tensor],
+                   k_weight: Optional[torch.Tensor], eps: float, v_other: Optional[torch.Tensor],
+                   mix: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                   positions: torch.Tensor, row_slot: torch.Tensor, page_size: int, fault: torch.Tensor) -> None:
+    """Between the projections and the cache of an attention layer.  A row of ``qkv`` holds ``nq`` query, ``nk``
+    key and ``nv`` value elements.  Queries (in place) and keys are divided by their root mean square over the
+    whole row part (eps inside the root) and multiplied by ``q_weight`` / ``k_weight`` (None: left alone);
+    values become ``(1 - mix) * v + mix * v_other`` (``v_other`` (n, nv), None: left alone); keys and values are
+    written into the row's place of ``k_pages`` / ``v_pages`` [pages, kv_heads, page_size, width]."""
+    lib = library()
+    n = qkv.shape[0]
+    kv_heads = k_pages.shape[1]
+    kps, khs = _page_strides(k_pages, nk // kv_heads)
+    vps, vhs = _page_strides(v_pages, nv // kv_heads)
+    _check(lib.tis_norm_mix_store(_dt(qkv), _p(qkv), qkv.stride(0), nq, nk, nv, _p(q_weight), _p(k_weight), _f(eps),
+                                  _p(v_other), v_other.stride(0) if v_other is not None else 0, _p(mix), _p(k_pages), kps,
+                                  khs, _p(v_pages), vps, vhs, kv_heads, page_size, k_pages.shape[0], _p(block_table),
+                                  block_table.stride(0), _p(positions), _p(row_slot), _p(fault), n, _stream()), lib)
+
+
+def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, k_pages: torch.Tensor,
+                     v_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
+                     num_heads: int, page_size: int, window: Optional[int], scale: float,
+                     bias_slope: Optional[torch.Tensor], bias_rate: Optional[torch.Tensor], fault: torch.Tensor,
+                     step=None) -> torch.Tensor:
+    """Attention of the step's rows over the paged cache with keys and values of any widths:
+    ``score = q . k * scale - bias_slope[h] * ln(1 + bias_rate[h] * distance)``, softmax over the keys
+    ``max(0, p - window + 1) .. p``, the result times ``sigmoid(gate)`` element by element.  ``q`` (n, H * k_dim),
+    ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free."""
+    lib = library()
+    n = q.shape[0]
+    kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
+    kps, khs = _page_strides(k_pages, k_dim)
+    vps, vhs = _page_strides(v_pages, v_dim)
+    _check(lib.tis_window_attention(_dt(q), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                    _p(out), out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs, _p(block_table),
+                                    block_table.stride(0), k_pages.shape[0], _p(positions), _p(row_slot), n, num_heads,
+                                    kv_heads, k_dim, v_dim, page_size, int(window or 0), _f(scale), _p(bias_slope),
+                                    _p(bias_rate), _p(fault), _stream()), lib)
+    return out
+
+
+def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, gate: Optional[torch.Tensor],
+               a_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float, unit_eps: float,
+               q_scale: float, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor,
+               num_heads: int, qk_heads: int, k_dim: int, v_dim: int) -> torch.Tensor:
+    """The delta rule with a decay per head and key channel over the rows of every request, from and into the
+    requests' states ``state`` (slots, H, k_dim, v_dim) float32 (a view with a free slot stride).  A row of ``qkv``:
+    queries and keys of ``qk_heads`` heads, values of ``num_heads`` heads.  Per head: q and k to unit length
+    (``unit_eps`` inside the root; q times ``q_scale``), beta = sigmoid(``beta``), decay = exp(-exp(a_log) *
+    softplus(``decay_in`` + dt_bias)) per key channel; S <- decay S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q; out = o / rms(o) * norm_weight * sigmoid(gate)."""
+    lib = library()
+    n = qkv.shape[0]
+    _check(lib.tis_delta_rule(_dt(qkv), _p(qkv), qkv.stride(0), _p(beta), beta.stride(0), _p(decay_in), decay_in.stride(0),
+                              _p(gate), gate.stride(0) if gate is not None else 0, _p(a_log), _p(dt_bias), _p(norm_weight),
+                              _f(eps), _f(unit_eps), _f(q_scale), _p(state), ctypes.c_size_t(state.stride(0)), _p(out),
+                              out.stride(0), _p(row_slot), _p(row_last), n, num_heads, qk_heads, k_dim, v_dim, _stream()),
+           lib)
     return out
 
 

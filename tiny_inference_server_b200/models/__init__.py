@@ -1,5 +1,6 @@
 """Registered architectures."""
 from .base import Model, ScheduleEntry, StepOutput
 from . import gqa_mtp  # noqa: F401  (registers "gqa_mtp_transformer")
+from . import kefisun  # noqa: F401  (registers "Kefisun")
 
 __all__ = ["Model", "ScheduleEntry", "StepOutput"]

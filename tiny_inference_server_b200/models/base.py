@@ -32,6 +32,9 @@ class ScheduleEntry:
     def state_spec(self) -> Optional[StateSpec]:
         return self.block.mixer.state_spec()
 
+    def filter_state_spec(self) -> Optional[StateSpec]:
+        return self.block.filter_state_spec()
+
 
 @dataclass
 class StepOutput:
@@ -86,6 +89,9 @@ class Model:
             s = e.state_spec()
             if s is not None:
                 out[f"entry{i}"] = s
+            s = e.filter_state_spec()
+            if s is not None:
+                out[f"entry{i}.filter"] = s
         out.update(self.extra_states(ctx))
         return out
 
@@ -110,6 +116,7 @@ class Model:
                 e.binding.kv_group = ref.group
             e.binding.kv_write = e.source is None
             e.binding.state = cache.states.get(f"entry{i}")
+            e.binding.filter_state = cache.states.get(f"entry{i}.filter")
 
     def forward(self, step, want_rows: torch.Tensor, aux: bool = False) -> StepOutput:
         raise NotImplementedError

@@ -3,13 +3,17 @@ their arrangement in a block, embedding and output head."""
 from .base import (BuildContext, FeedForward, KVSpec, LayerBinding, Mixer, Norm, Part, PositionEncoding,
                    StateSpec, WeightSpec)
 from .stream import ResidualStream
-from .norms import RMSNormL2
+from .norms import RMSNormL2, RMSNormMeanEps, RMSNormOnePlus
 from .positions import RotaryHalf, RotaryInterleaved
 from .attention import GqaAttention
-from .feed_forward import SwiGLU
+from .feed_forward import ClampedGLU, SwiGLU
+from .short_conv import CausalConv
+from .window_attention import BiasedWindowAttention, ValueShare
+from .delta_rule import ChannelDeltaRule
 from .block import Block
 from .embedding import Embedding, LMHead
 
 __all__ = ["BuildContext", "FeedForward", "KVSpec", "LayerBinding", "Mixer", "Norm", "Part",
-           "PositionEncoding", "StateSpec", "WeightSpec", "ResidualStream", "RMSNormL2", "RotaryHalf",
+           "PositionEncoding", "StateSpec", "WeightSpec", "ResidualStream", "RMSNormL2", "RMSNormMeanEps", "RMSNormOnePlus", "ClampedGLU", "CausalConv",
+           "BiasedWindowAttention", "ValueShare", "ChannelDeltaRule", "RotaryHalf",
            "RotaryInterleaved", "GqaAttention", "SwiGLU", "Block", "Embedding", "LMHead"]

@@ -57,8 +57,10 @@ class StateSpec:
 @dataclass
 class WeightSpec:
     shape: Tuple[int, ...]
-    init: str = "normal"              # "normal": N(0, std) ; "ones_normal": 1 + N(0, std)
+    init: str = "normal"              # "normal": N(0, std) ; "ones_normal": 1 + N(0, std) ; "uniform": U(lo, hi)
     dtype: Optional[torch.dtype] = None   # None: the model's storage dtype; int32 for integer tables
+    lo: float = 0.0
+    hi: float = 1.0
 
 
 @dataclass
@@ -79,6 +81,7 @@ class LayerBinding:
     kv_group: Optional[int] = None            # index of the plane's group (block tables, page size)
     kv_write: bool = True                     # False: the entry reads a plane that another entry fills
     state: Optional[torch.Tensor] = None      # [slots, *StateSpec.shape]
+    filter_state: Optional[torch.Tensor] = None   # the same for the block's input filter, if it keeps state
     k_pages: Optional[torch.Tensor] = None    # [pages, kv_heads, page_size, k_dim]: the key rows of every page
     v_pages: Optional[torch.Tensor] = None    # [pages, kv_heads, page_size, v_dim]: the value rows of every page
 

@@ -1,5 +1,8 @@
 """A pre-norm block: norm, mixer, residual; norm, feed-forward, residual
-(upstream ``Transformer_block``, main_models_new.py:139-152)."""
+(upstream ``Transformer_block``, main_models_new.py:139-152).  Two options that upstream's block does
+not have: an *input filter* between the first norm and the mixer (a part with ``forward(x, step, state)``,
+for instance a short convolution over time, with per-request state of its own), and no feed-forward
+at all (the block is its first sublayer only)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -9,20 +12,32 @@ from .stream import ResidualStream
 
 
 class Block(Part):
-    def __init__(self, norm_mixer, mixer, norm_ffn, ffn, prefix: str = ""):
+    def __init__(self, norm_mixer, mixer, norm_ffn, ffn, prefix: str = "", input_filter=None):
         super().__init__(prefix)
         self.norm_mixer = norm_mixer
         self.mixer = mixer
         self.norm_ffn = norm_ffn
         self.ffn = ffn
+        self.input_filter = input_filter
 
     def children(self):
-        return (self.norm_mixer, self.mixer, self.norm_ffn, self.ffn)
+        return tuple(p for p in (self.norm_mixer, self.input_filter, self.mixer, self.norm_ffn, self.ffn) if p is not None)
+
+    def filter_state_spec(self):
+        return self.input_filter.state_spec() if self.input_filter is not None else None
 
     def forward(self, stream: ResidualStream, step, binding: LayerBinding, following: Optional["Block"] = None) -> None:
         """``following``: the block that reads the stream after this one, if the caller knows it; its first
         norm can then be folded into this block's last product and that block's first one."""
         mixer, ffn = self.mixer, self.ffn
+        if self.input_filter is not None or ffn is None:
+            a = stream.normed(self.norm_mixer)
+            if self.input_filter is not None:
+                a = self.input_filter.forward(a, step, binding.filter_state)
+            stream.add(mixer.forward(a, step, binding))
+            if ffn is not None:
+                stream.add(ffn.forward(stream.normed(self.norm_ffn), step))
+            return
         a = stream.normed(self.norm_mixer, scaled=mixer.accepts_scaled_rows)
         if mixer.fuses_residual and ffn.accepts_scaled_rows:
             stream.add(mixer.forward(a, step, binding, residual=stream.sink(self.norm_ffn, a.dtype)))

@@ -10,11 +10,13 @@ from .base import BuildContext, Part, WeightSpec
 
 
 class Embedding(Part):
-    """``x = E[token]`` with no scaling (main_models_new.py:177-178,199).  The gathered rows
-    start the float32 residual stream."""
+    """``x = E[token] * scale`` (upstream has no scaling: main_models_new.py:177-178,199).  The gathered
+    rows start the float32 residual stream; the product with ``scale`` is made there, in 32-bit."""
 
-    def __init__(self, vocab: int, width: int, prefix: str = "", weight_name: str = "embedding.weight"):
+    def __init__(self, vocab: int, width: int, prefix: str = "", weight_name: str = "embedding.weight",
+                 scale: float = 1.0):
         super().__init__(prefix)
+        self.scale = float(scale)
         self.vocab = vocab
         self.width = width
         self.weight_name = weight_name
@@ -28,16 +30,18 @@ class Embedding(Part):
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         out = torch.empty((tokens.shape[0], self.width), dtype=torch.float32, device=tokens.device)
-        return ops.embed_rows(self.table, tokens, out)
+        return ops.embed_rows(self.table, tokens, out, self.scale)
 
 
 class LMHead(Part):
     """``logits = h @ E^T`` with the embedding matrix (tied, main_models_new.py:225-226) or
-    with a matrix of its own, ``lm_head.weight (vocab, width)``.  Logits are float32."""
+    with a matrix of its own, ``lm_head.weight (vocab, width)``.  Logits are float32; ``logit_scale``
+    multiplies them (the embedding's own scale plays no part here)."""
 
     def __init__(self, vocab: int, width: int, embedding: Optional[Embedding], prefix: str = "",
-                 weight_name: str = "lm_head.weight"):
+                 weight_name: str = "lm_head.weight", logit_scale: float = 1.0):
         super().__init__(prefix)
+        self.logit_scale = float(logit_scale)
         self.vocab = vocab
         self.width = width
         self.embedding = embedding            # given: tied
@@ -56,4 +60,7 @@ class LMHead(Part):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         wt = self.weight_t if self.embedding is None else self.embedding.table.t()
-        return ops.gemm_f32_out(h, wt)
+        logits = ops.gemm_f32_out(h, wt)
+        if self.logit_scale != 1.0:
+            ops.scale_f32(logits, self.logit_scale)
+        return logits

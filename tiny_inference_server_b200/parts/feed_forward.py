@@ -57,4 +57,50 @@ class SwiGLU(FeedForward):
         return ops.gemm(h, self.w_down, sink=residual)
 
 
+class ClampedGLU(FeedForward):
+    """``g = min(W_gate h + b, limit)``, ``u = clamp(W_up h + b, -limit, limit)``,
+    ``y = g * sigmoid(alpha * g) * (u + shift)``, output ``W_down y + b``.  Weights stored ``(out, in)``,
+    names ``gate, up, down`` with biases ``gate.b, up.b, down.b``.  On the device gate and up are one matrix;
+    the bias of the down projection is one more row of its matrix, met by a column of ones that the gating
+    kernel writes, so that the product adds it."""
+
+    def __init__(self, width: int, hidden: int, limit: float, alpha: float = 1.702, shift: float = 1.0,
+                 prefix: str = ""):
+        super().__init__(prefix)
+        self.width, self.hidden = width, hidden
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.padded = (hidden + 1 + 7) // 8 * 8
+        self.w_gate_up = self.w_down = self.b_gate = self.b_up = None
+
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int):
+        f = cfg.layers[layer_index]["mlp"]
+        return cls(cfg.hidden_size, f["ff"], f.get("limit", 0.0), prefix=prefix)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {
+            "gate": WeightSpec((self.hidden, self.width)), "gate.b": WeightSpec((self.hidden,)),
+            "up": WeightSpec((self.hidden, self.width)), "up.b": WeightSpec((self.hidden,)),
+            "down": WeightSpec((self.width, self.hidden)), "down.b": WeightSpec((self.width,)),
+        }
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        p = self.prefix
+        gu = torch.cat([tensors[p + "gate"], tensors[p + "up"]], dim=0).to(ctx.dtype).t()
+        self.w_gate_up = gu.to(ctx.device).contiguous()
+        down = torch.zeros((self.padded, self.width), dtype=ctx.dtype)
+        down[:self.hidden] = tensors[p + "down"].to(ctx.dtype).t()
+        down[self.hidden] = tensors[p + "down.b"].to(ctx.dtype)
+        self.w_down = down.to(ctx.device).contiguous()
+        self.b_gate = tensors[p + "gate.b"].to(device=ctx.device, dtype=torch.float32).contiguous()
+        self.b_up = tensors[p + "up.b"].to(device=ctx.device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, step=None):
+        gu = ops.gemm(x, self.w_gate_up)
+        y = torch.empty((x.shape[0], self.padded), dtype=x.dtype, device=x.device)
+        ops.glu_clamped(gu, self.b_gate, self.b_up, self.limit, self.alpha, self.shift, y, self.hidden)
+        return ops.gemm(y, self.w_down)
+
+
 register_part("ffn", "swiglu", SwiGLU)
+register_part("ffn", "clamped_glu", ClampedGLU)

@@ -46,4 +46,49 @@ class RMSNormL2(Norm):
         return ops.ResidualSink(values, self.scale, self.eps, norm=self)
 
 
+class RMSNormMeanEps(Norm):
+    """``y = x / sqrt(mean(x^2) + eps) * (offset + w)`` in float32, eps inside the root.  ``offset`` 1: the
+    stored tensor is the weight's distance from one; 0: it is the weight."""
+
+    def __init__(self, width: int, eps: float, prefix: str = "", weight_name: str = "weight", offset: float = 0.0):
+        super().__init__(prefix)
+        self.width = width
+        self.eps = float(eps)
+        self.weight_name = weight_name
+        self.offset = float(offset)
+        self.scale: Optional[torch.Tensor] = None
+        self.out_dtype = torch.float32
+
+    @classmethod
+    def from_config(cls, cfg, prefix: str):
+        return cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.width,), init="normal" if self.offset else "ones_normal")}
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        w = tensors[self.prefix + self.weight_name].to(device=ctx.device, dtype=torch.float32)
+        self.scale = (w + self.offset).contiguous()
+        self.out_dtype = ctx.dtype
+
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
+        return ops.add_rmsnorm(residual, delta, self.scale, self.eps, out, kind="mean_eps")
+
+    def forward(self, residual: torch.Tensor) -> torch.Tensor:
+        return self.add_norm(residual, None)
+
+    def sink(self, values: torch.Tensor):
+        return ops.ResidualSink(values, self.scale, self.eps, norm=self, kind="mean_eps")
+
+
+class RMSNormOnePlus(RMSNormMeanEps):
+    """``RMSNormMeanEps`` whose tensor holds the weight minus one: ``x / sqrt(mean(x^2) + eps) * (1 + w)``."""
+
+    def __init__(self, width: int, eps: float, prefix: str = "", weight_name: str = "weight"):
+        super().__init__(width, eps, prefix=prefix, weight_name=weight_name, offset=1.0)
+
+
 register_part("norm", "rmsnorm_l2", RMSNormL2)
+register_part("norm", "rmsnorm_mean_eps", RMSNormMeanEps)
+register_part("norm", "rmsnorm_one_plus", RMSNormOnePlus)

@@ -54,7 +54,12 @@ def part(kind: str, name: str) -> type:
 def config_from_folder(folder: str):
     """Read ``config.json`` and return the typed configuration of its architecture."""
     raw = read_config_json(folder)
-    return config_from_dict(raw)
+    cfg = config_from_dict(raw)
+    # sizes that config.json leaves to the tensors' shapes (only the files' headers are read)
+    if hasattr(cfg, "complete_from_shapes"):
+        from .weights.loader import read_shapes
+        cfg.complete_from_shapes(read_shapes(folder))
+    return cfg
 
 
 def config_from_dict(raw: dict):

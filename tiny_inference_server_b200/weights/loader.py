@@ -42,6 +42,26 @@ def read_safetensors(folder: str) -> Dict[str, torch.Tensor]:
     return out
 
 
+def read_shapes(folder: str) -> Dict[str, tuple]:
+    """Tensor name -> shape from the headers of the folder's safetensors files (no data is read).  A file is
+    an 8-byte little-endian length, that many bytes of JSON (name -> dtype, shape, data_offsets), then data."""
+    import json
+    import struct
+
+    out: Dict[str, tuple] = {}
+    for path in sorted(glob.glob(os.path.join(folder, "*.safetensors"))):
+        with open(path, "rb") as f:
+            head = f.read(8)
+            if len(head) != 8:
+                raise WeightError(f"{path}: not a safetensors file")
+            (size,) = struct.unpack("<Q", head)
+            meta = json.loads(f.read(size).decode("utf-8"))
+        for name, info in meta.items():
+            if name != "__metadata__":
+                out[name] = tuple(info["shape"])
+    return out
+
+
 def _normalise_dtype(name: str, t: torch.Tensor, problems: list) -> torch.Tensor:
     if t.dtype in (torch.bfloat16, torch.float32, torch.int32):
         return t

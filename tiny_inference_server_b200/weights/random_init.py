@@ -33,6 +33,8 @@ def random_tensors(expected: Dict[str, WeightSpec], seed: int, std: float = 0.02
         t = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * std
         if spec.init == "ones_normal":
             t = t + 1.0
+        elif spec.init == "uniform":
+            t = torch.rand(spec.shape, generator=gen, dtype=torch.float32) * (spec.hi - spec.lo) + spec.lo
         elif spec.init == "ones":
             t = torch.ones(spec.shape)
         elif spec.init == "zeros":
