@@ -71,10 +71,6 @@ def silu(x):
     return x * torch.sigmoid(x)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def distance_bias(r1, r2, L):
     """(H, L, L): r1_h * ln(1 + r2_h * (i - j)) for j <= i (0 elsewhere)."""
     i = torch.arange(L)

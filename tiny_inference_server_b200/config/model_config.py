@@ -8,6 +8,7 @@ are accepted as aliases of the lower-case keys.  No size is written into code.
 """
 from __future__ import annotations
 
+import copy
 import dataclasses
 import json
 import os
@@ -316,7 +317,7 @@ class KefisunConfig:
             if unknown:
                 parts.append("unknown keys: " + ", ".join(unknown))
             raise ConfigError(f"config for architecture {cls.architecture!r}: " + "; ".join(parts))
-        d = dict(vocab_size=raw["vocab"], hidden_size=raw["width"], layers=raw["layers"])
+        d = dict(vocab_size=raw["vocab"], hidden_size=raw["width"], layers=copy.deepcopy(raw["layers"]))
         if "norm" in raw:
             d["rms_norm_eps"] = float(raw["norm"]["eps"])
         if "embedding" in raw:
@@ -333,7 +334,7 @@ class KefisunConfig:
     def to_dict(self) -> dict:
         d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
              "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale,
-             "norm": {"eps": self.rms_norm_eps}, "layers": self.layers, "max_context": self.max_context,
+             "norm": {"eps": self.rms_norm_eps}, "layers": copy.deepcopy(self.layers), "max_context": self.max_context,
              "torch_dtype": self.torch_dtype}
         if self.canon_taps is not None:
             d["canon"] = {"taps": self.canon_taps}
