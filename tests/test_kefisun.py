@@ -339,6 +339,17 @@ def test_norms_embedding_gating(dtype):
     _close(ops.scale_f32(x, 0.3), want, 1e-6, "scaling")
 
 
+class _Step:
+    """What an attention kernel asks of a step, for one request's portion outside the engine."""
+    decode_only = False
+
+    def __init__(self, positions, row_slot):
+        self.positions, self.row_slot = positions, row_slot
+
+    def plan(self, planner):
+        return planner.infer(self.positions, self.row_slot)
+
+
 def _paged(n_pages, kv, page, k_dim, v_dim, dtype):
     kp = torch.full((n_pages, kv, page, k_dim), 1e4, dtype=DT[dtype], device="cuda")
     vp = torch.full((n_pages, kv, page, v_dim), 1e4, dtype=DT[dtype], device="cuda")
@@ -361,7 +372,8 @@ def _plain_attention(q, k, v, gate, H, G, scale, r1, r2, window):
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,kd,vd,window,page", [(4, 2, 16, 24, 9, 4), (6, 2, 48, 32, 40, 16), (2, 2, 8, 160, None, 8),
-                                                   (3, 1, 20, 12, 130, 16)])
+                                                   (3, 1, 20, 12, 130, 16), (4, 1, 32, 16, 70, 8), (2, 2, 128, 64, 100, 16),
+                                                   (2, 1, 16, 16, None, 16)])
 def test_window_attention_with_planted_keys(dtype, H, G, kd, vd, window, page):
     """norm + mix + store, then attention, in portions and single rows over scattered pages.  One key a few
     positions back and the keys at distance window - 1 and window from chosen rows are made to stand out (a
@@ -407,8 +419,9 @@ def test_window_attention_with_planted_keys(dtype, H, G, kd, vd, window, page):
     table = table.cuda()
     fault = torch.zeros(4, dtype=torch.int32, device="cuda")
     got = torch.zeros(L, H * vd, dtype=DT[dtype], device="cuda")
+    before = ops.calls["window_attention_mma"]
     fed = 0
-    cuts = [5, 2, 1, 1, 30, 2, 64]
+    cuts = [5, 2, 1, 1, 30, 2, 64, 100]
     i = 0
     while fed < L:
         n = min(cuts[i % len(cuts)], L - fed) if fed < L - 1 - 3 else 1
@@ -421,11 +434,14 @@ def test_window_attention_with_planted_keys(dtype, H, G, kd, vd, window, page):
         ops.norm_mix_store(qkv, nq, nk, nv, wq.cuda(), wk.cuda(), eps, v_other[rows].cuda(), lam.cuda(), kp, vp, table, pos,
                            slot, page, fault)
         out = torch.empty(n, H * vd, dtype=DT[dtype], device="cuda")
+        # portions as a step of the engine (in bfloat16, with widths that are multiples of 16: the tensor-core kernel)
         ops.window_attention(qkv[:, :nq], gate[rows].cuda(), out, kp, vp, table, pos, slot, H, page, window, scale,
-                             r1.cuda(), r2.cuda(), fault)
+                             r1.cuda(), r2.cuda(), fault, step=_Step(pos, slot) if n > 1 else None)
         got[rows] = out
         fed += n
     assert int(fault[0]) == 0
+    if dtype == "bfloat16" and kd % 16 == 0 and vd % 16 == 0:
+        assert ops.calls["window_attention_mma"] > before
     _close(got, ref, 4e-2 if dtype == "bfloat16" else 1e-4, "attention")
     # the planted keys matter: the plain result with a window one longer or shorter differs at those rows
     for w_off in (-1, 1):

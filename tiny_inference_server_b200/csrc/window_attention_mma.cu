@@ -1,0 +1,300 @@
+// Attention over a window of the paged cache on the tensor cores (bfloat16, mma.sync m16n8k16), for keys of
+// TIS_KD and values of TIS_VD elements (compiled per pair of widths):
+//   score = q . k * scale - r1[head] * ln(1 + r2[head] * distance),  keys pos - window < j <= pos,
+//   softmax in 32-bit, out = softmax . v * sigmoid(gate).
+// A CTA takes one tile of up to 64 consecutive rows of one request and one query head; each of its four warps
+// owns 16 rows and walks all keys the tile can see, 64 at a time, with the running maximum and sum of the rows in
+// registers.  Key and value rows are copied from their pages into shared memory by cp.async, two tiles in flight.
+// Scores, bias, maximum, sum and the output are 32-bit; the probabilities enter the second product as bfloat16
+// pairs (high part and remainder), so that the product sees them to 16 bits of mantissa.
+#include "common.cuh"
+
+#ifndef TIS_KD
+#define TIS_KD 64
+#endif
+#ifndef TIS_VD
+#define TIS_VD 64
+#endif
+
+namespace {
+
+constexpr int KD = TIS_KD, VD = TIS_VD;
+static_assert(KD % 16 == 0 && VD % 16 == 0, "key width and value width must be multiples of 16");
+constexpr int ROWS = 64, KEYS = 64, THREADS = 128;
+constexpr int QS = KD + 8, KS = KD + 8, VS = VD + 8;       // row strides in shared memory (elements): no bank conflicts
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+struct Params {
+    const bf16* q; int ldq;
+    const bf16* gate; int ldg;
+    bf16* out; int ldo;
+    const bf16* k_pages; size_t k_page_stride, k_head_stride;
+    const bf16* v_pages; size_t v_page_stride, v_head_stride;
+    const int* block_table; int bt_stride; int num_pages;
+    const int* positions; const int* row_slot;
+    const int* tile_row0; const int* tile_rows;
+    int H, G, page_size, window;
+    float scale;
+    const float* r1; const float* r2;
+    int* fault;
+};
+
+// Copies the key and value rows first .. first + 63 (those that exist: j <= last) of a request into a stage.
+__device__ __forceinline__ void load_tile(const Params& p, int slot, int kvh, int first, int last, bf16* ks, bf16* vs,
+                                          int* bad) {
+    constexpr int KC = KD / 8, VC = VD / 8;
+    for (int idx = threadIdx.x; idx < KEYS * (KC + VC); idx += THREADS) {
+        const int key = idx / (KC + VC), c = idx - key * (KC + VC);
+        const int j = first + key;
+        bf16* dst = c < KC ? ks + key * KS + c * 8 : vs + key * VS + (c - KC) * 8;
+        int page = -1;
+        if (j <= last) {
+            page = p.block_table[(size_t)slot * p.bt_stride + j / p.page_size];
+            if (page < 0 || page >= p.num_pages) { *bad = 1; page = -1; }
+        }
+        if (page >= 0) {
+            const int in_page = j % p.page_size;
+            const bf16* src = c < KC
+                ? p.k_pages + (size_t)page * p.k_page_stride + (size_t)kvh * p.k_head_stride + (size_t)in_page * KD + c * 8
+                : p.v_pages + (size_t)page * p.v_page_stride + (size_t)kvh * p.v_head_stride + (size_t)in_page * VD + (c - KC) * 8;
+            cp_async16(dst, src);
+        } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);      // keys that do not exist: finite zeros
+        }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS)
+window_attention_mma_kernel(const Params p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int bad;
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);              // [ROWS][QS]
+    bf16* kbuf = qs + ROWS * QS;                               // [2][KEYS][KS]
+    bf16* vbuf = kbuf + 2 * KEYS * KS;                         // [2][KEYS][VS]
+    pdl_launch_dependents();
+    const int tile = blockIdx.x, head = blockIdx.y;
+    const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
+    const int slot = p.row_slot[row0];
+    if (slot < 0 || nrows <= 0) return;
+    const int pos0 = p.positions[row0];
+    const int kvh = head / (p.H / p.G);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const float b1 = p.r1 != nullptr ? p.r1[head] : 0.f, b2 = p.r1 != nullptr ? p.r2[head] : 0.f;
+    if (tid == 0) bad = 0;
+    const int last = pos0 + nrows - 1;                         // the last key any row of the tile sees
+    const int first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int ntiles = (last - first) / KEYS + 1;
+    pdl_wait();
+    // queries of the tile (rows beyond nrows: zeros)
+    for (int idx = tid; idx < ROWS * (KD / 8); idx += THREADS) {
+        const int r = idx / (KD / 8), c = idx - r * (KD / 8);
+        bf16* dst = qs + r * QS + c * 8;
+        if (r < nrows) cp_async16(dst, p.q + (size_t)(row0 + r) * p.ldq + (size_t)head * KD + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();                                           // `bad` is initialised before any load may set it
+    load_tile(p, slot, kvh, first, last, kbuf, vbuf, &bad);
+    cp_async_commit();
+    float o[VD / 8][4];
+#pragma unroll
+    for (int n = 0; n < VD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    unsigned qf[KD / 16][4];
+    const int pos_a = pos0 + warp * 16 + g, pos_b = pos_a + 8;            // positions of this thread's two rows
+    const bool row_a = warp * 16 + g < nrows, row_b = warp * 16 + g + 8 < nrows;
+    for (int kt = 0; kt < ntiles; ++kt) {
+        const int stage = kt & 1;
+        if (kt + 1 < ntiles)
+            load_tile(p, slot, kvh, first + (kt + 1) * KEYS, last, kbuf + (stage ^ 1) * KEYS * KS, vbuf + (stage ^ 1) * KEYS * VS, &bad);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (kt == 0) {
+#pragma unroll
+            for (int kk = 0; kk < KD / 16; ++kk)
+                ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * QS + kk * 16 + 8 * (lane >> 4));
+        }
+        const bf16* ks = kbuf + stage * KEYS * KS;
+        const bf16* vs = vbuf + stage * KEYS * VS;
+        const int j0 = first + kt * KEYS;
+        // does this warp see any key of the tile?  (its rows: pos0 + 16 warp .. + 15)
+        const int w_lo = pos0 + warp * 16, w_hi = min(w_lo + 15, last);
+        const bool any = warp * 16 < nrows && j0 <= w_hi && (p.window <= 0 || j0 + KEYS - 1 > w_lo - p.window);
+        if (any) {
+            float s[KEYS / 8][4];
+#pragma unroll
+            for (int n = 0; n < KEYS / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < KD / 16; ++kk) {
+#pragma unroll
+                for (int n2 = 0; n2 < KEYS / 16; ++n2) {
+                    unsigned b[4];
+                    ldmatrix_x4(b, ks + (n2 * 16 + (lane & 7) + 8 * (lane >> 4)) * KS + kk * 16 + 8 * ((lane >> 3) & 1));
+                    mma_bf16(s[2 * n2], qf[kk], b[0], b[1]);
+                    mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+                }
+            }
+            // scale, bias, mask; the maximum of each row over the tile
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + n * 8 + 2 * t4 + (e & 1);
+                    const int pos = (e & 2) ? pos_b : pos_a;
+                    const bool ok = ((e & 2) ? row_b : row_a) && j <= pos && (p.window <= 0 || j > pos - p.window);
+                    float v = -INFINITY;
+                    if (ok) v = s[n][e] * p.scale - b1 * __logf(fmaf(b2, (float)(pos - j), 1.f));
+                    s[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m[h], mx[h]);
+                corr[h] = m[h] == -INFINITY ? 0.f : __expf(m[h] - m_new);
+                m[h] = m_new;
+            }
+            float sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float mm = m[e >> 1];
+                    const float pv = (s[n][e] == -INFINITY || mm == -INFINITY) ? 0.f : __expf(s[n][e] - mm);
+                    s[n][e] = pv;
+                    sum[e >> 1] += pv;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) l[h] = l[h] * corr[h] + sum[h];
+#pragma unroll
+            for (int n = 0; n < VD / 8; ++n) {
+                o[n][0] *= corr[0]; o[n][1] *= corr[0];
+                o[n][2] *= corr[1]; o[n][3] *= corr[1];
+            }
+            // out += P . V with P as bfloat16 high part + remainder
+#pragma unroll
+            for (int kk = 0; kk < KEYS / 16; ++kk) {
+                unsigned hi[4], lo[4];
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    const float x0 = s[2 * kk + (a >> 1)][(a & 1) * 2], x1 = s[2 * kk + (a >> 1)][(a & 1) * 2 + 1];
+                    const float h0 = __bfloat162float(__float2bfloat16_rn(x0)), h1 = __bfloat162float(__float2bfloat16_rn(x1));
+                    hi[a] = pack_bf16(h0, h1);
+                    lo[a] = pack_bf16(x0 - h0, x1 - h1);
+                }
+#pragma unroll
+                for (int n2 = 0; n2 < VD / 16; ++n2) {
+                    unsigned b[4];
+                    ldmatrix_x4_trans(b, vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * VS + n2 * 16 + 8 * (lane >> 4));
+                    mma_bf16(o[2 * n2], hi, b[0], b[1]);
+                    mma_bf16(o[2 * n2 + 1], hi, b[2], b[3]);
+                    mma_bf16(o[2 * n2], lo, b[0], b[1]);
+                    mma_bf16(o[2 * n2 + 1], lo, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                                       // the stage may be loaded again
+    }
+    cp_async_wait<0>();
+    if (bad && tid == 0) atomicExch(p.fault, 5);
+    // the sums of a row lie in the four threads that share it
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = warp * 16 + g + 8 * h;
+        if (r >= nrows) continue;
+        const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+        const size_t row = (size_t)(row0 + r);
+#pragma unroll
+        for (int n = 0; n < VD / 8; ++n) {
+            const int c = n * 8 + 2 * t4;
+            float x0 = o[n][2 * h] * inv, x1 = o[n][2 * h + 1] * inv;
+            if (p.gate != nullptr) {
+                const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.ldg + (size_t)head * VD + c);
+                x0 = x0 / (1.f + __expf(-__bfloat162float(gv.x)));
+                x1 = x1 / (1.f + __expf(-__bfloat162float(gv.y)));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(p.out + row * p.ldo + (size_t)head * VD + c) = __floats2bfloat162_rn(x0, x1);
+        }
+    }
+}
+
+}  // namespace
+
+TIS_API int tis_window_attention_mma_dims(int* kd, int* vd) {
+    *kd = KD;
+    *vd = VD;
+    return TIS_OK;
+}
+
+// Rows of q, gate and out must start on 16-byte (q) and 4-byte (gate, out) boundaries: ldq a multiple of 8,
+// ldg and ldo even; page rows on 16-byte boundaries (strides multiples of 8 elements).
+TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, int ldg, void* out, int ldo,
+                                     const void* k_pages, size_t k_page_stride, size_t k_head_stride,
+                                     const void* v_pages, size_t v_page_stride, size_t v_head_stride,
+                                     const int* block_table, int bt_stride, int num_pages, const int* positions,
+                                     const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
+                                     int H, int G, int page_size, int window, float scale, const float* r1,
+                                     const float* r2, int* fault, cudaStream_t stream) {
+    if (num_tiles <= 0) return TIS_OK;
+    if (H <= 0 || G <= 0 || H % G || page_size <= 0 || window < 0 || ldq % 8 || ldg % 2 || ldo % 2 ||
+        k_page_stride % 8 || k_head_stride % 8 || v_page_stride % 8 || v_head_stride % 8 ||
+        ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 || ((uintptr_t)gate | (uintptr_t)out) % 4) {
+        tis_set_error("window_attention_mma: %d query heads, %d kv heads, page size %d, window %d, row strides %d/%d/%d "
+                      "or an operand that is not aligned", H, G, page_size, window, ldq, ldg, ldo);
+        return TIS_BAD_SIZE;
+    }
+    Params p;
+    p.q = (const bf16*)q; p.ldq = ldq;
+    p.gate = (const bf16*)gate; p.ldg = ldg;
+    p.out = (bf16*)out; p.ldo = ldo;
+    p.k_pages = (const bf16*)k_pages; p.k_page_stride = k_page_stride; p.k_head_stride = k_head_stride;
+    p.v_pages = (const bf16*)v_pages; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride;
+    p.block_table = block_table; p.bt_stride = bt_stride; p.num_pages = num_pages;
+    p.positions = positions; p.row_slot = row_slot; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
+    p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.scale = scale; p.r1 = r1; p.r2 = r2; p.fault = fault;
+    const size_t smem = sizeof(bf16) * ((size_t)ROWS * QS + 2 * KEYS * KS + 2 * KEYS * VS);
+    static bool attr_set = false;
+    if (!attr_set && smem > 48 * 1024) {
+        cudaFuncSetAttribute(window_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    tis_launch(window_attention_mma_kernel, dim3(num_tiles, H), dim3(THREADS), smem, stream, p);
+    return tis_check_launch("window_attention_mma");
+}

@@ -42,10 +42,12 @@ def _nvcc() -> str:
 
 #: sources compiled once per head size (-DTIS_HD=<hd>) into libraries of their own
 PER_HEAD_SIZE = ("attention_mma.cu", "attention_tc.cu")
+#: sources compiled once per (key width, value width) (-DTIS_KD=<kd> -DTIS_VD=<vd>)
+PER_WIDTHS = ("window_attention_mma.cu",)
 
 
 def sources():
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu") and f not in PER_HEAD_SIZE)
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu") and f not in PER_HEAD_SIZE + PER_WIDTHS)
 
 
 def _digest() -> str:
@@ -134,6 +136,37 @@ def build_attention(head_dim: int) -> str:
     try:
         _say(f"compiling the attention kernels for head size {head_dim} (first call only)")
         jobs = [(src, os.path.join(work, src[:-3] + ".o"), (f"-DTIS_HD={head_dim}",)) for src in PER_HEAD_SIZE]
+        jobs.append(("errors.cu", os.path.join(work, "errors.o"), ()))
+        with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
+            list(ex.map(lambda j: _compile_one(nvcc, *j), jobs))
+        tmp_so = os.path.join(work, "lib.so")
+        p = subprocess.run([nvcc, "-shared", "-o", tmp_so, *[j[1] for j in jobs]], capture_output=True, text=True)
+        if p.returncode != 0:
+            raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
+        os.replace(tmp_so, out)
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    return out
+
+
+def window_attention_library_path(k_dim: int, v_dim: int) -> str:
+    return os.path.join(_build_root(), f"libtis_wattn_k{k_dim}_v{v_dim}_{_digest()}.so")
+
+
+def build_window_attention(k_dim: int, v_dim: int) -> str:
+    """The tensor-core kernel of windowed attention for one pair of key and value widths (compiled when a model
+    first needs it)."""
+    if k_dim % 16 or v_dim % 16 or not (16 <= k_dim <= 256) or not (16 <= v_dim <= 256):
+        raise BuildError(f"key width {k_dim}, value width {v_dim}: the kernel takes multiples of 16 from 16 to 256")
+    out = window_attention_library_path(k_dim, v_dim)
+    if os.path.isfile(out):
+        return out
+    nvcc = _nvcc()
+    root = os.path.dirname(out)
+    work = tempfile.mkdtemp(prefix="tis_obj_", dir=root)
+    try:
+        _say(f"compiling windowed attention for key width {k_dim}, value width {v_dim} (first call only)")
+        jobs = [(src, os.path.join(work, src[:-3] + ".o"), (f"-DTIS_KD={k_dim}", f"-DTIS_VD={v_dim}")) for src in PER_WIDTHS]
         jobs.append(("errors.cu", os.path.join(work, "errors.o"), ()))
         with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
             list(ex.map(lambda j: _compile_one(nvcc, *j), jobs))

@@ -827,6 +827,39 @@ def norm_mix_store(qkv: torch.Tensor, nq: int, nk: int, nv: int, q_weight: Optio
                                   block_table.stride(0), _p(positions), _p(row_slot), _p(fault), n, _stream()), lib)
 
 
+_wattn_libs = {}
+
+
+def window_attention_library(k_dim: int, v_dim: int):
+    """The tensor-core kernel of windowed attention for one pair of widths, compiled when first needed."""
+    lib = _wattn_libs.get((k_dim, v_dim))
+    if lib is None:
+        library()
+        lib = ctypes.CDLL(_build.build_window_attention(k_dim, v_dim))
+        lib.tis_last_error.restype = ctypes.c_char_p
+        kd, vd = ctypes.c_int(0), ctypes.c_int(0)
+        lib.tis_window_attention_mma_dims(ctypes.byref(kd), ctypes.byref(vd))
+        if (kd.value, vd.value) != (k_dim, v_dim):
+            raise KernelError(f"windowed attention library built for widths {kd.value}/{vd.value}, wanted {k_dim}/{v_dim}")
+        _wattn_libs[(k_dim, v_dim)] = lib
+    return lib
+
+
+#: steps with portions of prompts in bfloat16 run windowed attention on the tensor cores (tiles of up to 64 rows);
+#: TIS_WINDOW_ATTENTION_MMA=0 keeps every step on the CUDA-core kernel
+WINDOW_ATTENTION_MMA = os.environ.get("TIS_WINDOW_ATTENTION_MMA", "1") != "0"
+
+
+def window_attention_mma_usable(q: torch.Tensor, gate, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor) -> bool:
+    k_dim, v_dim = k_pages.shape[3], v_pages.shape[3]
+    return (WINDOW_ATTENTION_MMA and q.dtype == torch.bfloat16 and k_dim % 16 == 0 and v_dim % 16 == 0
+            and 16 <= k_dim <= 256 and 16 <= v_dim <= 256 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+            and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))
+            and all(s % 8 == 0 for s in (k_pages.stride(0), k_pages.stride(1), v_pages.stride(0), v_pages.stride(1)))
+            and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0)
+
+
 def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, k_pages: torch.Tensor,
                      v_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
                      num_heads: int, page_size: int, window: Optional[int], scale: float,
@@ -835,12 +868,30 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     """Attention of the step's rows over the paged cache with keys and values of any widths:
     ``score = q . k * scale - bias_slope[h] * ln(1 + bias_rate[h] * distance)``, softmax over the keys
     ``max(0, p - window + 1) .. p``, the result times ``sigmoid(gate)`` element by element.  ``q`` (n, H * k_dim),
-    ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free."""
+    ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free.
+
+    float32, decode steps and widths that are not multiples of 16: a CUDA-core kernel, a CTA per row and head.
+    bfloat16 steps that hold portions of prompts (``step`` given, with the tiles of ``kernels.window_plan``): the
+    tensor-core kernel, a CTA per tile of up to 64 rows and head."""
     lib = library()
     n = q.shape[0]
     kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
     kps, khs = _page_strides(k_pages, k_dim)
     vps, vhs = _page_strides(v_pages, v_dim)
+    if (step is not None and not getattr(step, "decode_only", False)
+            and window_attention_mma_usable(q, gate, out, k_pages, v_pages)):
+        from . import window_plan
+        row0, rows, count = step.plan(window_plan.planner())
+        wlib = window_attention_library(k_dim, v_dim)
+        calls["window_attention_mma"] += 1
+        _check(wlib.tis_window_attention_mma(_p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                             _p(out), out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs,
+                                             _p(block_table), block_table.stride(0), k_pages.shape[0], _p(positions),
+                                             _p(row_slot), _p(row0), _p(rows), count, num_heads, kv_heads, page_size,
+                                             int(window or 0), _f(scale), _p(bias_slope), _p(bias_rate), _p(fault),
+                                             _stream()), wlib)
+        return out
+    calls["window_attention"] += 1
     _check(lib.tis_window_attention(_dt(q), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                     _p(out), out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs, _p(block_table),
                                     block_table.stride(0), k_pages.shape[0], _p(positions), _p(row_slot), n, num_heads,

@@ -5,7 +5,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import ops, window_plan
 from ..registry import register_part
 from .base import BuildContext, KVSpec, LayerBinding, Mixer, StateSpec, WeightSpec
 from .short_conv import CausalConv
@@ -80,6 +80,10 @@ class BiasedWindowAttention(Mixer):
 
     def state_spec(self) -> Optional[StateSpec]:
         return self.conv.state_spec() if self.conv is not None else None
+
+    def step_planners(self):
+        # the tiles of rows that the tensor-core kernel takes
+        return (window_plan.planner(),)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs = {"q": WeightSpec((self.nq, self.width)), "k": WeightSpec((self.nk, self.width)),
