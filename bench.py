@@ -126,6 +126,8 @@ def device_random_tensors(specs, seed, device, std=0.02):
         t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=g)
         if spec.init == "ones_normal":
             t += 1.0
+        elif spec.init == "uniform":
+            t.uniform_(spec.lo, spec.hi, generator=g)
         out[name] = t.to(spec.dtype or torch.bfloat16)
     return out
 
@@ -284,6 +286,72 @@ def size_points(name, args, pk, count_ops):
     return out
 
 
+def kefisun_config(width, heads, kv_heads, ffn, vocab, layers, window):
+    """A Kefisun model with the layer sizes of a member of the GQA family: per four layers one delta-rule layer
+    and three of windowed attention, all with a feed-forward; head size 128 for keys and values."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+            "mask": {"size": window}, "v_mix": True}
+    delta = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+    ff = {"kind": "dense", "ff": ffn, "limit": 7.0}
+    return dict(architecture="Kefisun", vocab=vocab, width=width, canon={"taps": 4}, embedding={"scale": width ** 0.5},
+                logit_scale=1.0, norm={"eps": 1e-6}, max_context=8192,
+                layers=[{"type": "channel_delta" if i % 4 == 0 else "attention", "mixer": dict(delta if i % 4 == 0 else attn),
+                         "mlp": dict(ff)} for i in range(layers)])
+
+
+def compare_kefisun(args):
+    """``--compare kefisun``: prefill and decode of the Kefisun architecture beside the rotary GQA model at equal
+    layer sizes (same width, heads, feed-forward, vocabulary, number of layers, and the same window of keys), and
+    its kernels beside the like kernels of that model.  One JSON line; the default run is untouched."""
+    import gc
+    import types
+    import torch
+    from tiny_inference_server_b200.kernels import microbench, ops
+    from tiny_inference_server_b200.sampling import Sampler
+    pk = peaks()
+    count_ops = lambda: ops.launches  # noqa: E731
+    window, ctx, layers = 1024, 4096, 8
+    result = {"compare": "kefisun", "dtype": "bf16", "data": "synthetic", "layers": layers, "window": window, "context": ctx,
+              "peaks": pk, "sizes": {}}
+    for name in [x for x in args.compare_sizes.split(",") if x]:
+        base = SIZES[name][0]
+        twin = dict(base, num_layers=layers, num_mtp_heads=0, sliding_window=window, max_context=8192, tie_word_embeddings=True)
+        kef = kefisun_config(base["hidden_size"], base["num_heads"], base["num_kv_heads"], base["ffn_hidden"], base["vocab_size"],
+                             layers, window)
+        point = {}
+        for label, cfg_dict in (("kefisun", kef), ("gqa", twin)):
+            runner = None
+            try:
+                _, runner = build_runner(cfg_dict, ctx, 8, mtp=False)
+                steps = max(8, args.steps // 2)
+                r = {}
+                for b in (1, 8):
+                    ms, launches = decode_run(runner, b, ctx - steps - args.warmup - 2, steps, args.warmup, Sampler, count_ops)
+                    r[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    r[f"decode_b{b}_ms"] = round(ms, 4)
+                    r[f"decode_b{b}_launches"] = round(launches, 1)
+                best, first = prefill_run(runner, PREFILL_TOKENS, reps=2)
+                r["prefill_tok_s"] = round(PREFILL_TOKENS / (best * 1e-3), 1)
+                r["prefill_ms"] = round(best, 3)
+                r["prefill_first_run_ms"] = round(first, 3)
+                point[label] = r
+            except Exception as e:                       # noqa: BLE001
+                point[label] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            del runner
+            gc.collect()
+            torch.cuda.empty_cache()
+        margs = types.SimpleNamespace(width=base["hidden_size"], ffn=base["ffn_hidden"], heads=base["num_heads"],
+                                      kv_heads=base["num_kv_heads"], head_dim=128, page_size=PAGE, tokens=PREFILL_TOKENS, batch=8,
+                                      context=ctx, window=window)
+        try:
+            point["kernels"] = microbench.seqmix(margs)
+        except Exception as e:                           # noqa: BLE001
+            point["kernels"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        result["sizes"][name] = point
+    print(json.dumps(result))
+    return 0
+
+
 def reference_arm(args):
     """The upstream project's own code (an unmodified copy of its files under baseline/_ref: it is
     a folder of scripts, pip cannot install it) on the same metric: its Transformer with its own
@@ -376,9 +444,15 @@ def main(argv=None):
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, other contexts, MTP heads and prefill")
     ap.add_argument("--sizes", default="3b,8b", help="larger members of the family to measure too (3b, 8b; '' = none)")
+    ap.add_argument("--compare", default=None, choices=["kefisun"],
+                    help="instead of the default run: another architecture beside the GQA model at equal layer sizes")
+    ap.add_argument("--compare-sizes", default="0.9b,3b", help="with --compare: whose layer sizes (0.9b, 3b, 8b)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm(args)
+    if args.compare == "kefisun":
+        args.warmup = max(args.warmup, 3)
+        return compare_kefisun(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -89,6 +89,99 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w
         if (k < hist) st[(size_t)k * C + c] = h[k];
 }
 
+// The same for channel counts and row strides that are multiples of a 16-byte vector: a thread owns a (row, vector
+// of channels) and the taps are a template parameter, so that weights and history stay in registers.
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128)
+causal_conv_vec_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ state,
+                       size_t state_stride, T* __restrict__ out, int ldo, const int* __restrict__ row_slot,
+                       const int* __restrict__ row_last, int n, int C, int residual, int act_silu) {
+    constexpr int N = Vec16<T>::N, HIST = TAPS - 1;
+    pdl_launch_dependents();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * N;
+    const int r = blockIdx.y;
+    if (c >= C) return;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    int back = 0;
+    while (back < HIST && r - back - 1 >= 0 && row_slot[r - back - 1] == slot) ++back;
+    if (back > 0 && back < HIST) return;              // computed by the thread of the request's first row
+    float wt[N][TAPS];
+#pragma unroll
+    for (int e = 0; e < N; ++e)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wt[e][j] = w[(size_t)(c + e) * TAPS + j];
+    pdl_wait();
+    auto finish = [&](float (&acc)[N], const float (&cur)[N], size_t row) {
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+            if (residual) acc[e] += cur[e];
+            if (act_silu) acc[e] = acc[e] / (1.f + expf(-acc[e]));
+        }
+        Vec16<T>::store(out + row * ldo + c, acc);
+    };
+    if (back == HIST) {
+        float acc[N], cur[N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            Vec16<T>::load(x + (size_t)(r - HIST + j) * ldx + c, cur);
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc[e] = fmaf(wt[e][j], cur[e], acc[e]);
+        }
+        finish(acc, cur, (size_t)r);
+        return;
+    }
+    const int rows = row_last[r] - r + 1;
+    float* st = state + (size_t)slot * state_stride;
+    float h[HIST > 0 ? HIST : 1][N];
+#pragma unroll
+    for (int k = 0; k < HIST; ++k)
+#pragma unroll
+        for (int e = 0; e < N; ++e) h[k][e] = st[(size_t)k * C + c + e];
+    const int mine = rows < HIST ? rows : HIST;
+    for (int i = 0; i < mine; ++i) {
+        float acc[N], cur[N];
+        Vec16<T>::load(x + (size_t)(r + i) * ldx + c, cur);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+            float a = 0.f;                              // the taps in the order of the other path: bit-equal results
+#pragma unroll
+            for (int k = 0; k < HIST; ++k) a = fmaf(wt[e][k], h[k][e], a);
+            acc[e] = fmaf(wt[e][HIST], cur[e], a);
+        }
+#pragma unroll
+        for (int k = 0; k + 1 < HIST; ++k)
+#pragma unroll
+            for (int e = 0; e < N; ++e) h[k][e] = h[k + 1][e];
+        if (HIST > 0) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) h[HIST - 1][e] = cur[e];
+        }
+        finish(acc, cur, (size_t)(r + i));
+    }
+    if (rows > HIST) {
+#pragma unroll
+        for (int k = 0; k < HIST; ++k) Vec16<T>::load(x + (size_t)(r + rows - HIST + k) * ldx + c, h[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < HIST; ++k)
+#pragma unroll
+        for (int e = 0; e < N; ++e) st[(size_t)k * C + c + e] = h[k][e];
+}
+
+template <typename T, int TAPS>
+static void launch_causal_conv_vec(const T* x, int ldx, const float* w, float* state, size_t state_stride, T* out, int ldo,
+                                   const int* row_slot, const int* row_last, int n, int C, int residual, int act_silu,
+                                   cudaStream_t stream) {
+    constexpr int N = Vec16<T>::N;
+    const int vecs = C / N;
+    const int threads = vecs >= 128 ? 128 : (vecs + 31) / 32 * 32;
+    tis_launch(causal_conv_vec_kernel<T, TAPS>, dim3((vecs + threads - 1) / threads, n), dim3(threads), 0, stream, x, ldx, w,
+               state, state_stride, out, ldo, row_slot, row_last, n, C, residual, act_silu);
+}
+
 TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, float* state, size_t state_stride,
                             void* out, int ldo, const int* row_slot, const int* row_last, int n, int C, int taps,
                             int residual, int act_silu, cudaStream_t stream) {
@@ -100,6 +193,23 @@ TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, f
     if (x == out) {
         tis_set_error("causal_conv: a row reads the rows before it, so the result needs a place of its own");
         return TIS_BAD_SIZE;
+    }
+    const int per = dtype == TIS_BF16 ? 8 : 4;
+    if (taps >= 2 && taps <= 5 && C % per == 0 && ldx % per == 0 && ldo % per == 0 &&
+        ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+#define TIS_CONV_CASE(K)                                                                                               \
+    case K:                                                                                                            \
+        TIS_DISPATCH_DTYPE(dtype, T, launch_causal_conv_vec<T, K>((const T*)x, ldx, w, state, state_stride, (T*)out,   \
+            ldo, row_slot, row_last, n, C, residual, act_silu, stream));                                               \
+        break;
+        switch (taps) {
+            TIS_CONV_CASE(2)
+            TIS_CONV_CASE(3)
+            TIS_CONV_CASE(4)
+            TIS_CONV_CASE(5)
+        }
+#undef TIS_CONV_CASE
+        return tis_check_launch("causal_conv");
     }
     TIS_DISPATCH_DTYPE(dtype, T,
         tis_launch(causal_conv_kernel<T>, dim3((C + 127) / 128, n), dim3(128), 0, stream, (const T*)x, ldx, w, state,

@@ -2,11 +2,14 @@
 // TIS_KD and values of TIS_VD elements (compiled per pair of widths):
 //   score = q . k * scale - r1[head] * ln(1 + r2[head] * distance),  keys pos - window < j <= pos,
 //   softmax in 32-bit, out = softmax . v * sigmoid(gate).
-// A CTA takes one tile of up to 64 consecutive rows of one request and one query head; each of its four warps
-// owns 16 rows and walks all keys the tile can see, 64 at a time, with the running maximum and sum of the rows in
-// registers.  Key and value rows are copied from their pages into shared memory by cp.async, two tiles in flight.
-// Scores, bias, maximum, sum and the output are 32-bit; the probabilities enter the second product as bfloat16
-// pairs (high part and remainder), so that the product sees them to 16 bits of mantissa.
+// A CTA takes one tile of consecutive rows of one request and one kv head, with all the query heads that share
+// the kv head: row r and query head h of the group are packed row r * (H / G) + h of a block of 64 packed rows, so
+// that a key or value row is brought into shared memory once for all of them.  Tiles of many rows: each of the four
+// warps owns 16 packed rows and walks all keys the tile can see, 64 at a time, with the running maximum and sum of
+// its rows in registers.  Tiles of at most 16 packed rows (decode rows): the four warps share the rows and take
+// every fourth tile of keys each; their partial results are merged through shared memory.  Key and value rows are
+// copied from their pages by cp.async, two tiles in flight.  Scores, bias, maximum, sum and the output are 32-bit;
+// the probabilities enter the second product rounded to bfloat16.
 #include "common.cuh"
 
 #ifndef TIS_KD
@@ -98,25 +101,37 @@ window_attention_mma_kernel(const Params p) {
     bf16* kbuf = qs + ROWS * QS;                               // [2][KEYS][KS]
     bf16* vbuf = kbuf + 2 * KEYS * KS;                         // [2][KEYS][VS]
     pdl_launch_dependents();
-    const int tile = blockIdx.x, head = blockIdx.y;
+    const int tile = blockIdx.x, kvh = blockIdx.y;
     const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
     const int slot = p.row_slot[row0];
     if (slot < 0 || nrows <= 0) return;
     const int pos0 = p.positions[row0];
-    const int kvh = head / (p.H / p.G);
+    const int gq = p.H / p.G;                                  // query heads that share the kv head
+    const int packed = nrows * gq;                             // packed rows in use (<= 64)
+    const bool split_keys = packed <= 16;                      // the warps share the rows and split the key tiles
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
-    const float b1 = p.r1 != nullptr ? p.r1[head] : 0.f, b2 = p.r1 != nullptr ? p.r2[head] : 0.f;
     if (tid == 0) bad = 0;
     const int last = pos0 + nrows - 1;                         // the last key any row of the tile sees
     const int first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int ntiles = (last - first) / KEYS + 1;
+    const int base = split_keys ? 0 : warp * 16;               // first packed row of this warp
+    // this thread's two packed rows: base + g and base + g + 8
+    const int m_a = base + g, m_b = m_a + 8;
+    const bool row_a = m_a < packed, row_b = m_b < packed;
+    const int pos_a = pos0 + m_a / gq, pos_b = pos0 + m_b / gq;
+    const int head_a = kvh * gq + m_a % gq, head_b = kvh * gq + m_b % gq;
+    float b1_a = 0.f, b2_a = 0.f, b1_b = 0.f, b2_b = 0.f;
+    if (p.r1 != nullptr) {
+        if (row_a) { b1_a = p.r1[head_a]; b2_a = p.r2[head_a]; }
+        if (row_b) { b1_b = p.r1[head_b]; b2_b = p.r2[head_b]; }
+    }
     pdl_wait();
-    // queries of the tile (rows beyond nrows: zeros)
+    // queries of the tile (packed rows beyond those in use: zeros)
     for (int idx = tid; idx < ROWS * (KD / 8); idx += THREADS) {
-        const int r = idx / (KD / 8), c = idx - r * (KD / 8);
-        bf16* dst = qs + r * QS + c * 8;
-        if (r < nrows) cp_async16(dst, p.q + (size_t)(row0 + r) * p.ldq + (size_t)head * KD + c * 8);
+        const int m = idx / (KD / 8), c = idx - m * (KD / 8);
+        bf16* dst = qs + m * QS + c * 8;
+        if (m < packed) cp_async16(dst, p.q + (size_t)(row0 + m / gq) * p.ldq + (size_t)(kvh * gq + m % gq) * KD + c * 8);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();                                           // `bad` is initialised before any load may set it
@@ -127,8 +142,8 @@ window_attention_mma_kernel(const Params p) {
     for (int n = 0; n < VD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     unsigned qf[KD / 16][4];
-    const int pos_a = pos0 + warp * 16 + g, pos_b = pos_a + 8;            // positions of this thread's two rows
-    const bool row_a = warp * 16 + g < nrows, row_b = warp * 16 + g + 8 < nrows;
+    // positions of the first and last row among this warp's packed rows
+    const int w_lo = pos0 + base / gq, w_hi = min(pos0 + (base + 15) / gq, last);
     for (int kt = 0; kt < ntiles; ++kt) {
         const int stage = kt & 1;
         if (kt + 1 < ntiles)
@@ -139,14 +154,14 @@ window_attention_mma_kernel(const Params p) {
         if (kt == 0) {
 #pragma unroll
             for (int kk = 0; kk < KD / 16; ++kk)
-                ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * QS + kk * 16 + 8 * (lane >> 4));
+                ldmatrix_x4(qf[kk], qs + (base + (lane & 7) + 8 * ((lane >> 3) & 1)) * QS + kk * 16 + 8 * (lane >> 4));
         }
         const bf16* ks = kbuf + stage * KEYS * KS;
         const bf16* vs = vbuf + stage * KEYS * VS;
         const int j0 = first + kt * KEYS;
-        // does this warp see any key of the tile?  (its rows: pos0 + 16 warp .. + 15)
-        const int w_lo = pos0 + warp * 16, w_hi = min(w_lo + 15, last);
-        const bool any = warp * 16 < nrows && j0 <= w_hi && (p.window <= 0 || j0 + KEYS - 1 > w_lo - p.window);
+        // does this warp see any key of the tile?
+        bool any = base < packed && j0 <= w_hi && (p.window <= 0 || j0 + KEYS - 1 > w_lo - p.window);
+        if (split_keys) any = any && (kt & 3) == warp;
         if (any) {
             float s[KEYS / 8][4];
 #pragma unroll
@@ -171,7 +186,7 @@ window_attention_mma_kernel(const Params p) {
                     const int pos = (e & 2) ? pos_b : pos_a;
                     const bool ok = ((e & 2) ? row_b : row_a) && j <= pos && (p.window <= 0 || j > pos - p.window);
                     float v = -INFINITY;
-                    if (ok) v = s[n][e] * p.scale - b1 * __logf(fmaf(b2, (float)(pos - j), 1.f));
+                    if (ok) v = s[n][e] * p.scale - ((e & 2) ? b1_b : b1_a) * __logf(fmaf((e & 2) ? b2_b : b2_a, (float)(pos - j), 1.f));
                     s[n][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -203,25 +218,19 @@ window_attention_mma_kernel(const Params p) {
                 o[n][0] *= corr[0]; o[n][1] *= corr[0];
                 o[n][2] *= corr[1]; o[n][3] *= corr[1];
             }
-            // out += P . V with P as bfloat16 high part + remainder
+            // out += P . V
 #pragma unroll
             for (int kk = 0; kk < KEYS / 16; ++kk) {
-                unsigned hi[4], lo[4];
+                unsigned pa[4];
 #pragma unroll
-                for (int a = 0; a < 4; ++a) {
-                    const float x0 = s[2 * kk + (a >> 1)][(a & 1) * 2], x1 = s[2 * kk + (a >> 1)][(a & 1) * 2 + 1];
-                    const float h0 = __bfloat162float(__float2bfloat16_rn(x0)), h1 = __bfloat162float(__float2bfloat16_rn(x1));
-                    hi[a] = pack_bf16(h0, h1);
-                    lo[a] = pack_bf16(x0 - h0, x1 - h1);
-                }
+                for (int a = 0; a < 4; ++a)
+                    pa[a] = pack_bf16(s[2 * kk + (a >> 1)][(a & 1) * 2], s[2 * kk + (a >> 1)][(a & 1) * 2 + 1]);
 #pragma unroll
                 for (int n2 = 0; n2 < VD / 16; ++n2) {
                     unsigned b[4];
                     ldmatrix_x4_trans(b, vs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * VS + n2 * 16 + 8 * (lane >> 4));
-                    mma_bf16(o[2 * n2], hi, b[0], b[1]);
-                    mma_bf16(o[2 * n2 + 1], hi, b[2], b[3]);
-                    mma_bf16(o[2 * n2], lo, b[0], b[1]);
-                    mma_bf16(o[2 * n2 + 1], lo, b[2], b[3]);
+                    mma_bf16(o[2 * n2], pa, b[0], b[1]);
+                    mma_bf16(o[2 * n2 + 1], pa, b[2], b[3]);
                 }
             }
         }
@@ -235,22 +244,59 @@ window_attention_mma_kernel(const Params p) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
     }
+    if (split_keys) {
+        // merge the four warps' partial results of the 16 packed rows (the key and value stages are free now)
+        float* part = reinterpret_cast<float*>(kbuf);          // [4 warps][16 rows][VD + 2]: out, maximum, sum
+        constexpr int PS = VD + 2;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float* dst = part + ((size_t)warp * 16 + g + 8 * h) * PS;
+#pragma unroll
+            for (int n = 0; n < VD / 8; ++n) {
+                dst[n * 8 + 2 * t4] = o[n][2 * h];
+                dst[n * 8 + 2 * t4 + 1] = o[n][2 * h + 1];
+            }
+            if (t4 == 0) { dst[VD] = m[h]; dst[VD + 1] = l[h]; }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < packed * VD; idx += THREADS) {
+            const int mrow = idx / VD, c = idx - mrow * VD;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, part[((size_t)w * 16 + mrow) * PS + VD]);
+            float num = 0.f, den = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* src = part + ((size_t)w * 16 + mrow) * PS;
+                const float f = src[VD] == -INFINITY ? 0.f : __expf(src[VD] - mm);
+                num = fmaf(src[c], f, num);
+                den = fmaf(src[VD + 1], f, den);
+            }
+            float x = den > 0.f ? num / den : 0.f;
+            const size_t row = (size_t)(row0 + mrow / gq);
+            const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
+            if (p.gate != nullptr) x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + col])));
+            p.out[row * p.ldo + col] = __float2bfloat16_rn(x);
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const int r = warp * 16 + g + 8 * h;
-        if (r >= nrows) continue;
+        const int mrow = base + g + 8 * h;
+        if (mrow >= packed) continue;
         const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
-        const size_t row = (size_t)(row0 + r);
+        const size_t row = (size_t)(row0 + mrow / gq);
+        const size_t col0 = (size_t)(kvh * gq + mrow % gq) * VD;
 #pragma unroll
         for (int n = 0; n < VD / 8; ++n) {
             const int c = n * 8 + 2 * t4;
             float x0 = o[n][2 * h] * inv, x1 = o[n][2 * h + 1] * inv;
             if (p.gate != nullptr) {
-                const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.ldg + (size_t)head * VD + c);
+                const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.ldg + col0 + c);
                 x0 = x0 / (1.f + __expf(-__bfloat162float(gv.x)));
                 x1 = x1 / (1.f + __expf(-__bfloat162float(gv.y)));
             }
-            *reinterpret_cast<__nv_bfloat162*>(p.out + row * p.ldo + (size_t)head * VD + c) = __floats2bfloat162_rn(x0, x1);
+            *reinterpret_cast<__nv_bfloat162*>(p.out + row * p.ldo + col0 + c) = __floats2bfloat162_rn(x0, x1);
         }
     }
 }
@@ -263,7 +309,7 @@ TIS_API int tis_window_attention_mma_dims(int* kd, int* vd) {
     return TIS_OK;
 }
 
-// Rows of q, gate and out must start on 16-byte (q) and 4-byte (gate, out) boundaries: ldq a multiple of 8,
+// Tiles hold at most 64 / (H / G) rows.  Rows of q, gate and out must start on 16-byte (q) and 4-byte (gate, out) boundaries: ldq a multiple of 8,
 // ldg and ldo even; page rows on 16-byte boundaries (strides multiples of 8 elements).
 TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, int ldg, void* out, int ldo,
                                      const void* k_pages, size_t k_page_stride, size_t k_head_stride,
@@ -273,7 +319,7 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
                                      int H, int G, int page_size, int window, float scale, const float* r1,
                                      const float* r2, int* fault, cudaStream_t stream) {
     if (num_tiles <= 0) return TIS_OK;
-    if (H <= 0 || G <= 0 || H % G || page_size <= 0 || window < 0 || ldq % 8 || ldg % 2 || ldo % 2 ||
+    if (H <= 0 || G <= 0 || H % G || H / G > ROWS || page_size <= 0 || window < 0 || ldq % 8 || ldg % 2 || ldo % 2 ||
         k_page_stride % 8 || k_head_stride % 8 || v_page_stride % 8 || v_head_stride % 8 ||
         ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 || ((uintptr_t)gate | (uintptr_t)out) % 4) {
         tis_set_error("window_attention_mma: %d query heads, %d kv heads, page size %d, window %d, row strides %d/%d/%d "
@@ -295,6 +341,6 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
         cudaFuncSetAttribute(window_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_set = true;
     }
-    tis_launch(window_attention_mma_kernel, dim3(num_tiles, H), dim3(THREADS), smem, stream, p);
+    tis_launch(window_attention_mma_kernel, dim3(num_tiles, G), dim3(THREADS), smem, stream, p);
     return tis_check_launch("window_attention_mma");
 }

@@ -7,6 +7,8 @@
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 4096     (tcgen05 kernel, above 64 rows)
     python -m tiny_inference_server_b200.kernels.microbench prefill --tokens 2048 --layers 4
     python -m tiny_inference_server_b200.kernels.microbench sampling --rows 8 --vocab 49152
+    python -m tiny_inference_server_b200.kernels.microbench seqmix --window 1024   (windowed attention, short
+        convolution, delta rule and gating, each beside the like kernel of the rotary GQA model)
     python -m tiny_inference_server_b200.kernels.microbench all
 
 ``--reps N --no-timing`` launches the kernel N times and exits (a profiler attaches to that);
@@ -157,6 +159,141 @@ def rowwise(args):
                                                 fault), 12)
     mb = n * ((H + 2 * KVH) * hd * 2 + (H + 2 * KVH) * hd * 2) / 1e6
     print(f"rope_kv_write  {n} rows: {t:7.2f} us  {mb / t * 1e3:7.1f} GB/s")
+
+
+class _PortionStep:
+    """A step that holds one portion of a prompt (or ``decode``: one row per request), with whatever a planner
+    makes of its device arrays."""
+
+    def __init__(self, positions, row_slot, decode=False):
+        self.positions, self.row_slot, self.decode_only = positions, row_slot, decode
+        self.max_position = int(positions.max())
+        self.min_position = int(positions.min())
+        self._plans = {}
+
+    def plan(self, planner):
+        if planner.key not in self._plans:
+            self._plans[planner.key] = planner.infer(self.positions, self.row_slot)
+        return self._plans[planner.key]
+
+
+def seqmix(args, hbm_gbs=None, tflops=None):
+    """The kernels of the mixers that are not rotary attention, each beside the kernel of the rotary GQA model
+    that does the like work at equal sizes (``None``: that model has none).  Returns {name: {us, rate, unit,
+    like_us, like_rate}}; ``rate`` is GB/s of the bytes the kernel must move, or TFLOP/s for the prompt attention."""
+    from .attention_plan import infer_tiles
+    dev = "cuda"
+    d, F, H, G, hd, page = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.page_size
+    n, B, ctx, W = args.tokens, args.batch, args.context, args.window
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    i32 = dict(device=dev, dtype=torch.int32)
+    fault = torch.zeros(4, **i32)
+    out = {}
+
+    def put(name, us, work, unit, like_us=None, like_work=None):
+        e = {"us": round(us, 2), "rate": round(work / us / 1e3, 1) if unit == "GB/s" else round(work / us / 1e6, 1), "unit": unit}
+        if like_us is not None:
+            lw = work if like_work is None else like_work
+            e["like_us"] = round(like_us, 2)
+            e["like_rate"] = round(lw / like_us / 1e3, 1) if unit == "GB/s" else round(lw / like_us / 1e6, 1)
+        out[name] = e
+        like = f"   like kernel {e['like_us']:9.2f} us {e['like_rate']:9.1f} {unit}" if like_us is not None else ""
+        print(f"{name:34s} {e['us']:9.2f} us {e['rate']:9.1f} {unit}{like}")
+
+    # ---- attention over a prompt portion: n rows of one request from position 0, window W
+    num_pages = (n + page - 1) // page
+    planes = [torch.randn(num_pages, 2, G, page, hd, **bf) for _ in range(2)]
+    table = torch.arange(num_pages, **i32).reshape(1, num_pages).contiguous()
+    pos = torch.arange(n, **i32)
+    slot = torch.zeros(n, **i32)
+    q = torch.randn(n, (H + 2 * G) * hd, **bf)
+    gate = torch.randn(n, H * hd, **bf)
+    o = torch.empty(n, H * hd, **bf)
+    r1 = torch.rand(H, device=dev) + 0.2
+    r2 = torch.rand(H, device=dev) + 0.1
+    step = _PortionStep(pos, slot)
+    pairs = sum(min(p + 1, W) for p in range(n))
+    flops = 4.0 * H * hd * pairs
+    t_new = _graph_time(lambda i: ops.window_attention(q, gate, o, planes[i % 2][:, 0], planes[i % 2][:, 1], table, pos, slot, H,
+                                                       page, W, hd ** -0.5, r1, r2, fault, step), 10)
+    gstep = _Step(infer_tiles(pos, slot, H // G), n - 1)
+    gstep.decode_only = False
+    gstep.min_position = 0
+    t_like = _graph_time(lambda i: ops.paged_attention(q, o, planes[i % 2], table, pos, slot, H, G, hd, page, W, fault, gstep), 10)
+    put(f"attention, {n} rows, window {W}", t_new, flops, "TFLOP/s", t_like)
+    # ---- attention of B decode rows at position ctx - 1
+    pages_per = (ctx + page - 1) // page
+    n_planes = max(2, min(12, (300 << 20) // max(1, B * ctx * 2 * G * hd * 2)))
+    planes = [torch.randn(B * pages_per, 2, G, page, hd, **bf) for _ in range(n_planes)]
+    table = torch.arange(B * pages_per, **i32).reshape(B, pages_per).contiguous()
+    pos = torch.full((B,), ctx - 1, **i32)
+    slot = torch.arange(B, **i32)
+    qd, gd, od = q[:B].contiguous(), gate[:B].contiguous(), torch.empty(B, H * hd, **bf)
+    dstep = _PortionStep(pos, slot, decode=True)
+    kv_bytes = B * min(W, ctx) * 2 * G * hd * 2
+    t_new = _graph_time(lambda i: ops.window_attention(qd, gd, od, planes[i % n_planes][:, 0], planes[i % n_planes][:, 1], table,
+                                                       pos, slot, H, page, W, hd ** -0.5, r1, r2, fault, dstep))
+    gstep = _Step(infer_tiles(pos, slot, H // G), ctx - 1)
+    t_like = _graph_time(lambda i: ops.paged_attention(qd, od, planes[i % n_planes], table, pos, slot, H, G, hd, page, W, fault,
+                                                       gstep))
+    put(f"attention, {B} decode rows, window {W}", t_new, kv_bytes, "GB/s", t_like)
+    del planes
+    # ---- between the projections and the cache
+    bufs = 4
+    num_pages = (n + page - 1) // page
+    plane = torch.zeros(num_pages, 2, G, page, hd, **bf)
+    table = torch.arange(num_pages, **i32).reshape(1, num_pages).contiguous()
+    pos = torch.arange(n, **i32)
+    slot = torch.zeros(n, **i32)
+    last = torch.full((n,), n - 1, **i32)
+    nq, nk = H * hd, G * hd
+    qkv = [torch.randn(n, nq + 2 * nk, **bf) for _ in range(bufs)]
+    other = torch.randn(n, nk, **bf)
+    wq, wk, lam = torch.ones(nq, device=dev), torch.ones(nk, device=dev), torch.full((1,), 0.3, device=dev)
+    t_new = _graph_time(lambda i: ops.norm_mix_store(qkv[i % bufs], nq, nk, nk, wq, wk, 1e-6, other, lam, plane[:, 0], plane[:, 1],
+                                                     table, pos, slot, page, fault), 12)
+    cos, sin = torch.ones(n, hd // 2, device=dev), torch.zeros(n, hd // 2, device=dev)
+    t_like = _graph_time(lambda i: ops.rope_kv_write(qkv[i % bufs], pos, slot, cos, sin, plane, table, H, G, hd, page, fault), 12)
+    moved = n * (nq + 2 * nk) * 2 * 2
+    put(f"norm, mix, cache write, {n} rows", t_new, moved + n * nk * 2, "GB/s", t_like, moved)
+    # ---- short convolutions: the mixer's input (with the residual) and its projections
+    state = torch.zeros(2, 3 * (nq + 2 * nk), device=dev)
+    x = [torch.randn(n, d, **bf) for _ in range(bufs)]
+    y = torch.empty(n, d, **bf)
+    w4 = torch.randn(d, 4, device=dev)
+    t_new = _graph_time(lambda i: ops.causal_conv(x[i % bufs], w4, state, y, slot, last, residual=True), 12)
+    res = [torch.randn(n, d, device=dev) for _ in range(bufs)]
+    ones = torch.ones(d, device=dev)
+    t_like = _graph_time(lambda i: ops.add_rmsnorm(res[i % bufs], x[i % bufs], ones, 1e-6, y, kind="mean_eps"), 12)
+    put(f"input convolution, {n} x {d}", t_new, n * d * 4, "GB/s", t_like, n * d * 12)
+    yc = torch.empty(n, nq + 2 * nk, **bf)
+    wc = torch.randn(nq + 2 * nk, 4, device=dev)
+    t_new = _graph_time(lambda i: ops.causal_conv(qkv[i % bufs], wc, state, yc, slot, last, silu=True), 12)
+    put(f"convolution of q, k, v, {n} rows", t_new, n * (nq + 2 * nk) * 4, "GB/s")
+    # ---- gating of the feed-forward
+    gu = [torch.randn(n, 2 * F, **bf) for _ in range(bufs)]
+    hid = torch.empty(n, F + 8, **bf)
+    bg, bu = torch.zeros(F, device=dev), torch.zeros(F, device=dev)
+    t_new = _graph_time(lambda i: ops.glu_clamped(gu[i % bufs], bg, bu, 7.0, 1.702, 1.0, hid, F), 12)
+    hid2 = torch.empty(n, F, **bf)
+    t_like = _graph_time(lambda i: ops.swiglu(gu[i % bufs], hid2, 32), 12)
+    put(f"gating, {n} x {F}", t_new, n * F * 6, "GB/s", t_like)
+    # ---- the delta rule: a prompt portion, and B decode rows
+    nv = H * hd
+    rows = [torch.randn(n, 2 * nk + nv, **bf) for _ in range(2)]
+    beta, a, gt = torch.randn(n, H, **bf), torch.randn(n, H * hd, **bf), torch.randn(n, nv, **bf)
+    a_log, dtb, nw = torch.zeros(H, device=dev), torch.zeros(H * hd, device=dev), torch.ones(hd, device=dev)
+    st = torch.zeros(max(B, 1), H * hd * hd, device=dev)
+    od = torch.empty(n, nv, **bf)
+    t_new = _graph_time(lambda i: ops.delta_rule(rows[i % 2], beta, a, gt, a_log, dtb, nw, 1e-6, 1e-6, hd ** -0.5, st, od, slot, last,
+                                                 H, G, hd, hd), 4)
+    put(f"delta rule, {n} rows of one request", t_new, 6.0 * n * H * hd * hd, "TFLOP/s")
+    slot_b = torch.arange(B, **i32)
+    t_new = _graph_time(lambda i: ops.delta_rule(rows[i % 2][:B], beta[:B], a[:B], gt[:B], a_log, dtb, nw, 1e-6, 1e-6, hd ** -0.5, st,
+                                                 od[:B], slot_b, slot_b, H, G, hd, hd), 12)
+    put(f"delta rule, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s")
+    return out
+
 
 
 def sampling(args):
@@ -362,7 +499,8 @@ def timeline(args):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
     ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "sampling", "timeline",
-                                     "all"])
+                                     "seqmix", "all"])
+    ap.add_argument("--window", type=int, default=1024, help="seqmix: keys a row sees")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8)
@@ -402,6 +540,8 @@ def main(argv=None):
         prefill(args)
     if args.what in ("sampling", "all"):
         sampling(args)
+    if args.what in ("seqmix", "all"):
+        seqmix(args)
     return 0
 
 

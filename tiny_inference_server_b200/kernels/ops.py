@@ -845,7 +845,7 @@ def window_attention_library(k_dim: int, v_dim: int):
     return lib
 
 
-#: steps with portions of prompts in bfloat16 run windowed attention on the tensor cores (tiles of up to 64 rows);
+#: bfloat16 steps run windowed attention on the tensor cores;
 #: TIS_WINDOW_ATTENTION_MMA=0 keeps every step on the CUDA-core kernel
 WINDOW_ATTENTION_MMA = os.environ.get("TIS_WINDOW_ATTENTION_MMA", "1") != "0"
 
@@ -870,18 +870,17 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     ``max(0, p - window + 1) .. p``, the result times ``sigmoid(gate)`` element by element.  ``q`` (n, H * k_dim),
     ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free.
 
-    float32, decode steps and widths that are not multiples of 16: a CUDA-core kernel, a CTA per row and head.
-    bfloat16 steps that hold portions of prompts (``step`` given, with the tiles of ``kernels.window_plan``): the
-    tensor-core kernel, a CTA per tile of up to 64 rows and head."""
+    float32, and widths that are not multiples of 16: a CUDA-core kernel, a CTA per row and head.  bfloat16 inside
+    a step (``step`` given, with the tiles of ``kernels.window_plan``): the tensor-core kernel, a CTA per tile of rows
+    and kv head; the warps of a decode row's CTA split its keys."""
     lib = library()
     n = q.shape[0]
     kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
     kps, khs = _page_strides(k_pages, k_dim)
     vps, vhs = _page_strides(v_pages, v_dim)
-    if (step is not None and not getattr(step, "decode_only", False)
-            and window_attention_mma_usable(q, gate, out, k_pages, v_pages)):
+    if step is not None and num_heads // kv_heads <= 64 and window_attention_mma_usable(q, gate, out, k_pages, v_pages):
         from . import window_plan
-        row0, rows, count = step.plan(window_plan.planner())
+        row0, rows, count = step.plan(window_plan.planner(num_heads // kv_heads))
         wlib = window_attention_library(k_dim, v_dim)
         calls["window_attention_mma"] += 1
         _check(wlib.tis_window_attention_mma(_p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,

@@ -83,7 +83,7 @@ class BiasedWindowAttention(Mixer):
 
     def step_planners(self):
         # the tiles of rows that the tensor-core kernel takes
-        return (window_plan.planner(),)
+        return (window_plan.planner(self.num_heads // self.kv_heads),)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs = {"q": WeightSpec((self.nq, self.width)), "k": WeightSpec((self.nk, self.width)),
