@@ -116,7 +116,7 @@ def _segments(row_slot):
 
 
 def causal_conv(x, weight, state, out, row_slot, row_last, residual=False, silu=False):
-    c, taps = weight.shape
+    taps, c = weight.shape
     hist = taps - 1
     for r0, rows, slot in _segments(row_slot):
         assert int(row_last[r0]) == r0 + rows - 1
@@ -124,7 +124,7 @@ def causal_conv(x, weight, state, out, row_slot, row_last, residual=False, silu=
         seq = torch.cat([old, x[r0:r0 + rows].to(torch.float32)], dim=0)          # positions -hist .. rows-1
         y = torch.zeros((rows, c), dtype=torch.float32)
         for j in range(taps):
-            y += weight[:, j] * seq[j:j + rows]
+            y += weight[j] * seq[j:j + rows]
         if residual:
             y += seq[hist:]
         if silu:

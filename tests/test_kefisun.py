@@ -297,7 +297,7 @@ def test_causal_conv_in_portions(dtype, taps, silu, residual):
         x = torch.cat([xs[0][fed[0]:fed[0] + cuts[0]], xs[1][fed[1]:fed[1] + cuts[1]]]).cuda()
         out = torch.empty_like(x)
         row_slot, row_last = _rows(cuts, [2, 0])
-        ops.causal_conv(x, w.cuda(), state, out, row_slot, row_last, residual=residual, silu=silu)
+        ops.causal_conv(x, w.t().contiguous().cuda(), state, out, row_slot, row_last, residual=residual, silu=silu)
         got[0][fed[0]:fed[0] + cuts[0]] = out[:cuts[0]]
         got[1][fed[1]:fed[1] + cuts[1]] = out[cuts[0]:]
         fed = [fed[0] + cuts[0], fed[1] + cuts[1]]

@@ -12,7 +12,8 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------------------------
-// y[r, c] = (residual ? x[r, c] : 0) + sum_j w[c, j] * x(t - taps + 1 + j)[c], optionally through silu.
+// y[r, c] = (residual ? x[r, c] : 0) + sum_j w[j, c] * x(t - taps + 1 + j)[c], optionally through silu (the weights
+// lie tap by tap: [taps][C]).
 // x(t') of a position before this step's rows of the request comes from the request's state, which holds its
 // last taps-1 inputs (oldest first, zero before the start of the sequence) and is brought up to date here.
 //
@@ -39,7 +40,7 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w
     if (back > 0 && back < hist) return;              // computed by the thread of the request's first row
     float wt[CONV_MAX_TAPS];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)j * C + c] : 0.f;
     pdl_wait();
     if (back == hist) {                               // every input is a row of this step (or there is no history)
         float acc = 0.f, cur = 0.f;
@@ -108,9 +109,12 @@ causal_conv_vec_kernel(const T* __restrict__ x, int ldx, const float* __restrict
     if (back > 0 && back < HIST) return;              // computed by the thread of the request's first row
     float wt[N][TAPS];
 #pragma unroll
-    for (int e = 0; e < N; ++e)
+    for (int j = 0; j < TAPS; ++j)
 #pragma unroll
-        for (int j = 0; j < TAPS; ++j) wt[e][j] = w[(size_t)(c + e) * TAPS + j];
+        for (int e = 0; e < N; e += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(w + (size_t)j * C + c + e);
+            wt[e][j] = v.x; wt[e + 1][j] = v.y; wt[e + 2][j] = v.z; wt[e + 3][j] = v.w;
+        }
     pdl_wait();
     auto finish = [&](float (&acc)[N], const float (&cur)[N], size_t row) {
 #pragma unroll
@@ -196,7 +200,7 @@ TIS_API int tis_causal_conv(int dtype, const void* x, int ldx, const float* w, f
     }
     const int per = dtype == TIS_BF16 ? 8 : 4;
     if (taps >= 2 && taps <= 5 && C % per == 0 && ldx % per == 0 && ldo % per == 0 &&
-        ((uintptr_t)x | (uintptr_t)out) % 16 == 0) {
+        ((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) % 16 == 0) {
 #define TIS_CONV_CASE(K)                                                                                               \
     case K:                                                                                                            \
         TIS_DISPATCH_DTYPE(dtype, T, launch_causal_conv_vec<T, K>((const T*)x, ldx, w, state, state_stride, (T*)out,   \
@@ -581,6 +585,138 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
     }
 }
 
+// The same recurrence with more parallelism, for value widths that are multiples of 32 and key widths 4 * D4: a CTA
+// takes 32 columns of one head's state, four lanes share a column (lane p keeps the key channels p * D4 .. + D4 - 1 of
+// it in registers) and add their partial sums with two shuffles.  The chunk's q^, k^ and g lie in shared memory with
+// four floats of padding after every quarter, so that the four lanes of a column read different banks with 16-byte
+// loads.  The outputs leave unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
+template <typename T, int D4>
+__global__ void __launch_bounds__(128)
+delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
+                        int lda, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
+                        float q_scale, float* __restrict__ state, size_t state_stride, float* __restrict__ o_raw,
+                        const int* __restrict__ row_slot, const int* __restrict__ row_last, int H, int G, int v_dim) {
+    constexpr int KDIM = 4 * D4, QP = D4 + 4, ROW = 4 * QP, COLS = 32;
+    __shared__ __align__(16) float qs[DELTA_CHUNK][ROW];
+    __shared__ __align__(16) float ks[DELTA_CHUNK][ROW];
+    __shared__ __align__(16) float gs[DELTA_CHUNK][ROW];
+    __shared__ float vs[DELTA_CHUNK][COLS];
+    __shared__ float betas[DELTA_CHUNK];
+    pdl_launch_dependents();
+    const int r0 = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
+    const int slot = row_slot[r0];
+    if (slot < 0) return;
+    if (r0 > 0 && row_slot[r0 - 1] == slot) return;
+    const int rows = row_last[r0] - r0 + 1;
+    const int kvh = head / (H / G);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int col = tid >> 2, part = tid & 3;
+    const float decay_rate = expf(A_log[head]);
+    float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
+    float S[D4];
+    pdl_wait();
+#pragma unroll
+    for (int i = 0; i < D4; ++i) S[i] = S_glob[(size_t)(part * D4 + i) * v_dim];
+    const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = 2 * G * KDIM + head * v_dim + col0;
+    const int nv = H * v_dim;
+    for (int c0 = 0; c0 < rows; c0 += DELTA_CHUNK) {
+        const int cnt = min(DELTA_CHUNK, rows - c0);
+        __syncthreads();
+        for (int t = warp; t < cnt; t += 4) {
+            const T* row = qkv + (size_t)(r0 + c0 + t) * ld;
+            float sq = 0.f, sk = 0.f;
+            for (int i = lane; i < KDIM; i += 32) {
+                const float qv = to_f32(row[q_off + i]), kv = to_f32(row[k_off + i]);
+                sq += qv * qv;
+                sk += kv * kv;
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.f / sqrtf(sk + unit_eps);
+            for (int i = lane; i < KDIM; i += 32) {
+                const int at = i + (i / D4) * 4;
+                qs[t][at] = to_f32(row[q_off + i]) * fq;
+                ks[t][at] = to_f32(row[k_off + i]) * fk;
+                const float a = to_f32(a_in[(size_t)(r0 + c0 + t) * lda + head * KDIM + i]) + dt_bias[head * KDIM + i];
+                gs[t][at] = expf(-decay_rate * softplus_f(a));
+            }
+            vs[t][lane] = to_f32(row[v_off + lane]);
+            if (lane == 0) betas[t] = 1.f / (1.f + expf(-to_f32(b_in[(size_t)(r0 + c0 + t) * ldb + head])));
+        }
+        __syncthreads();
+        for (int t = 0; t < cnt; ++t) {
+            const float4* kt = reinterpret_cast<const float4*>(&ks[t][part * QP]);
+            const float4* qt = reinterpret_cast<const float4*>(&qs[t][part * QP]);
+            const float4* gt = reinterpret_cast<const float4*>(&gs[t][part * QP]);
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < D4 / 4; ++i) {
+                const float4 gv = gt[i], kv = kt[i];
+                S[4 * i] *= gv.x; S[4 * i + 1] *= gv.y; S[4 * i + 2] *= gv.z; S[4 * i + 3] *= gv.w;
+                d0 = fmaf(S[4 * i], kv.x, d0); d1 = fmaf(S[4 * i + 1], kv.y, d1);
+                d2 = fmaf(S[4 * i + 2], kv.z, d2); d3 = fmaf(S[4 * i + 3], kv.w, d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            const float u = betas[t] * (vs[t][col] - dot);
+            d0 = d1 = d2 = d3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < D4 / 4; ++i) {
+                const float4 kv = kt[i], qv = qt[i];
+                S[4 * i] = fmaf(kv.x, u, S[4 * i]); S[4 * i + 1] = fmaf(kv.y, u, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(kv.z, u, S[4 * i + 2]); S[4 * i + 3] = fmaf(kv.w, u, S[4 * i + 3]);
+                d0 = fmaf(S[4 * i], qv.x, d0); d1 = fmaf(S[4 * i + 1], qv.y, d1);
+                d2 = fmaf(S[4 * i + 2], qv.z, d2); d3 = fmaf(S[4 * i + 3], qv.w, d3);
+            }
+            float o = (d0 + d1) + (d2 + d3);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (part == 0) o_raw[(size_t)(r0 + c0 + t) * nv + head * v_dim + col0 + col] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < D4; ++i) S_glob[(size_t)(part * D4 + i) * v_dim] = S[i];
+}
+
+// out[r, head, :] = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate) for every (row, head): a warp each.
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gate, int ldg, const float* __restrict__ norm_w,
+                      float eps, T* __restrict__ out, int ldo, const int* __restrict__ row_slot, int n, int H, int v_dim) {
+    pdl_launch_dependents();
+    const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (idx >= n * H) return;
+    const int r = idx / H, head = idx - r * H;
+    if (row_slot[r] < 0) return;
+    pdl_wait();
+    const float* o = o_raw + (size_t)r * H * v_dim + (size_t)head * v_dim;
+    float ss = 0.f;
+    for (int j = lane; j < v_dim; j += 32) ss += o[j] * o[j];
+    ss = warp_sum(ss);
+    const float f = rsqrtf(ss / (float)v_dim + eps);
+    for (int j = lane; j < v_dim; j += 32) {
+        float x = o[j] * f * norm_w[j];
+        if (gate != nullptr) x = x / (1.f + expf(-to_f32(gate[(size_t)r * ldg + head * v_dim + j])));
+        out[(size_t)r * ldo + head * v_dim + j] = from_f32<T>(x);
+    }
+}
+
+template <typename T, int D4>
+static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb, const T* a_in, int lda, const T* gate, int ldg,
+                                   const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
+                                   float q_scale, float* state, size_t state_stride, T* out, int ldo, float* o_raw,
+                                   const int* row_slot, const int* row_last, int n, int H, int G, int v_dim,
+                                   cudaStream_t stream) {
+    tis_launch(delta_rule_split_kernel<T, D4>, dim3(n, H, v_dim / 32), dim3(128), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
+               dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, H, G, v_dim);
+    int st = tis_check_launch("delta_rule");
+    if (st != TIS_OK) return st;
+    tis_launch(delta_out_norm_kernel<T>, dim3((n * H + 3) / 4), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps,
+               out, ldo, row_slot, n, H, v_dim);
+    return tis_check_launch("delta_out_norm");
+}
+
 template <typename T, int DIM>
 static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const T* a_in, int lda, const T* gate, int ldg,
                              const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
@@ -601,12 +737,37 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
     return tis_check_launch("delta_rule");
 }
 
+// Whether tis_delta_rule takes the kernel that splits a head's columns over CTAs for these widths (it then needs
+// `o_raw`, n * H * v_dim floats of scratch).
+TIS_API int tis_delta_rule_splits(int k_dim, int v_dim) {
+    if (v_dim % 32) return 0;
+    switch (k_dim) { case 16: case 32: case 48: case 64: case 96: case 128: return 1; default: return 0; }
+}
+
 TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in, int ldb, const void* a_in, int lda,
                            const void* gate, int ldg, const float* A_log, const float* dt_bias, const float* norm_w,
                            float eps, float unit_eps, float q_scale, float* state, size_t state_stride, void* out,
-                           int ldo, const int* row_slot, const int* row_last, int n, int H, int G, int k_dim, int v_dim,
-                           cudaStream_t stream) {
+                           int ldo, float* o_raw, const int* row_slot, const int* row_last, int n, int H, int G,
+                           int k_dim, int v_dim, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
+    if (o_raw != nullptr && H > 0 && G > 0 && H % G == 0 && tis_delta_rule_splits(k_dim, v_dim)) {
+#define TIS_DELTA_SPLIT(D)                                                                                             \
+    case 4 * D:                                                                                                        \
+        TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule_split<T, D>((const T*)qkv, ld, (const T*)b_in, ldb,      \
+            (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state,           \
+            state_stride, (T*)out, ldo, o_raw, row_slot, row_last, n, H, G, v_dim, stream));                           \
+        break;
+        switch (k_dim) {
+            TIS_DELTA_SPLIT(4)
+            TIS_DELTA_SPLIT(8)
+            TIS_DELTA_SPLIT(12)
+            TIS_DELTA_SPLIT(16)
+            TIS_DELTA_SPLIT(24)
+            TIS_DELTA_SPLIT(32)
+            default: break;
+        }
+#undef TIS_DELTA_SPLIT
+    }
     if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > 256) {
         tis_set_error("delta_rule: %d heads, %d query/key heads, key width %d, value width %d (at most 256)", H, G, k_dim,
                       v_dim);

@@ -68,28 +68,34 @@ struct Params {
     int* fault;
 };
 
-// Copies the key and value rows first .. first + 63 (those that exist: j <= last) of a request into a stage.
+// Copies the key and value rows first .. first + 63 (those that exist: j <= last) of a request into a stage.  Two
+// threads share a key: one look-up of its page, then every other 16-byte chunk of its two rows each.
 __device__ __forceinline__ void load_tile(const Params& p, int slot, int kvh, int first, int last, bf16* ks, bf16* vs,
                                           int* bad) {
     constexpr int KC = KD / 8, VC = VD / 8;
-    for (int idx = threadIdx.x; idx < KEYS * (KC + VC); idx += THREADS) {
-        const int key = idx / (KC + VC), c = idx - key * (KC + VC);
-        const int j = first + key;
-        bf16* dst = c < KC ? ks + key * KS + c * 8 : vs + key * VS + (c - KC) * 8;
-        int page = -1;
-        if (j <= last) {
-            page = p.block_table[(size_t)slot * p.bt_stride + j / p.page_size];
-            if (page < 0 || page >= p.num_pages) { *bad = 1; page = -1; }
-        }
-        if (page >= 0) {
-            const int in_page = j % p.page_size;
-            const bf16* src = c < KC
-                ? p.k_pages + (size_t)page * p.k_page_stride + (size_t)kvh * p.k_head_stride + (size_t)in_page * KD + c * 8
-                : p.v_pages + (size_t)page * p.v_page_stride + (size_t)kvh * p.v_head_stride + (size_t)in_page * VD + (c - KC) * 8;
-            cp_async16(dst, src);
-        } else {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);      // keys that do not exist: finite zeros
-        }
+    static_assert(THREADS == 2 * KEYS, "two threads a key");
+    const int key = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int j = first + key;
+    bf16* kd = ks + key * KS;
+    bf16* vd = vs + key * VS;
+    int page = -1;
+    if (j <= last) {
+        page = p.block_table[(size_t)slot * p.bt_stride + j / p.page_size];
+        if (page < 0 || page >= p.num_pages) { *bad = 1; page = -1; }
+    }
+    if (page >= 0) {
+        const int in_page = j % p.page_size;
+        const bf16* ksrc = p.k_pages + (size_t)page * p.k_page_stride + (size_t)kvh * p.k_head_stride + (size_t)in_page * KD;
+        const bf16* vsrc = p.v_pages + (size_t)page * p.v_page_stride + (size_t)kvh * p.v_head_stride + (size_t)in_page * VD;
+#pragma unroll
+        for (int c = 0; c < KC / 2; ++c) cp_async16(kd + (2 * c + half) * 8, ksrc + (2 * c + half) * 8);
+#pragma unroll
+        for (int c = 0; c < VC / 2; ++c) cp_async16(vd + (2 * c + half) * 8, vsrc + (2 * c + half) * 8);
+    } else {                                                  // keys that do not exist: finite zeros
+#pragma unroll
+        for (int c = 0; c < KC / 2; ++c) *reinterpret_cast<uint4*>(kd + (2 * c + half) * 8) = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int c = 0; c < VC / 2; ++c) *reinterpret_cast<uint4*>(vd + (2 * c + half) * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
 }
 

@@ -260,14 +260,14 @@ def seqmix(args, hbm_gbs=None, tflops=None):
     state = torch.zeros(2, 3 * (nq + 2 * nk), device=dev)
     x = [torch.randn(n, d, **bf) for _ in range(bufs)]
     y = torch.empty(n, d, **bf)
-    w4 = torch.randn(d, 4, device=dev)
+    w4 = torch.randn(4, d, device=dev)
     t_new = _graph_time(lambda i: ops.causal_conv(x[i % bufs], w4, state, y, slot, last, residual=True), 12)
     res = [torch.randn(n, d, device=dev) for _ in range(bufs)]
     ones = torch.ones(d, device=dev)
     t_like = _graph_time(lambda i: ops.add_rmsnorm(res[i % bufs], x[i % bufs], ones, 1e-6, y, kind="mean_eps"), 12)
     put(f"input convolution, {n} x {d}", t_new, n * d * 4, "GB/s", t_like, n * d * 12)
     yc = torch.empty(n, nq + 2 * nk, **bf)
-    wc = torch.randn(nq + 2 * nk, 4, device=dev)
+    wc = torch.randn(4, nq + 2 * nk, device=dev)
     t_new = _graph_time(lambda i: ops.causal_conv(qkv[i % bufs], wc, state, yc, slot, last, silu=True), 12)
     put(f"convolution of q, k, v, {n} rows", t_new, n * (nq + 2 * nk) * 4, "GB/s")
     # ---- gating of the feed-forward

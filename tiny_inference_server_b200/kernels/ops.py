@@ -786,14 +786,16 @@ def scale_f32(x: torch.Tensor, scale: float) -> torch.Tensor:
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
                 row_last: torch.Tensor, residual: bool = False, silu: bool = False) -> torch.Tensor:
-    """A causal convolution over time on each channel: ``out[r, c] = (x[r, c] if residual) + sum_j weight[c, j] *
-    x(t - taps + 1 + j)[c]``, through silu if asked.  ``x`` (n, C) with a free row stride; ``weight`` (C, taps)
-    float32; ``state`` (slots, taps - 1, C) float32 (a view with a free slot stride): the last inputs of every
+    """A causal convolution over time on each channel: ``out[r, c] = (x[r, c] if residual) + sum_j weight[j, c] *
+    x(t - taps + 1 + j)[c]``, through silu if asked.  ``x`` (n, C) with a free row stride; ``weight`` (taps, C)
+    float32 (tap by tap, so that neighbouring channels are neighbours in memory); ``state`` (slots, taps - 1, C) float32 (a view with a free slot stride): the last inputs of every
     request, oldest first, zero before the start of a sequence; read for the rows whose history lies before this
     step and brought up to date."""
     lib = library()
     n, c = x.shape
-    taps = weight.shape[1]
+    taps = weight.shape[0]
+    if weight.shape[1] != c or not weight.is_contiguous():
+        raise KernelError(f"causal_conv: weights {tuple(weight.shape)} for {c} channels (wanted contiguous (taps, channels))")
     _check(lib.tis_causal_conv(_dt(x), _p(x), x.stride(0), _p(weight), _p(state), ctypes.c_size_t(state.stride(0)),
                                _p(out), out.stride(0), _p(row_slot), _p(row_last), n, c, taps, int(residual), int(silu),
                                _stream()), lib)
@@ -911,11 +913,18 @@ def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, ga
     o = S^T q; out = o / rms(o) * norm_weight * sigmoid(gate)."""
     lib = library()
     n = qkv.shape[0]
+    # widths that the kernel with a head's columns split over CTAs takes: the outputs pass through 32-bit scratch
+    # and a second launch normalises them
+    raw = None
+    if lib.tis_delta_rule_splits(k_dim, v_dim):
+        raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qkv.device)
+        global launches
+        launches += 1
     _check(lib.tis_delta_rule(_dt(qkv), _p(qkv), qkv.stride(0), _p(beta), beta.stride(0), _p(decay_in), decay_in.stride(0),
                               _p(gate), gate.stride(0) if gate is not None else 0, _p(a_log), _p(dt_bias), _p(norm_weight),
                               _f(eps), _f(unit_eps), _f(q_scale), _p(state), ctypes.c_size_t(state.stride(0)), _p(out),
-                              out.stride(0), _p(row_slot), _p(row_last), n, num_heads, qk_heads, k_dim, v_dim, _stream()),
-           lib)
+                              out.stride(0), _p(raw), _p(row_slot), _p(row_last), n, num_heads, qk_heads, k_dim, v_dim,
+                              _stream()), lib)
     return out
 
 

@@ -44,7 +44,7 @@ class CausalConv(Part):
 
     def load(self, tensors, ctx: BuildContext) -> None:
         w = torch.cat([tensors[self.prefix + name].to(torch.float32) for name in self.weight_names], dim=0)
-        self.weight = w.to(ctx.device).contiguous()
+        self.weight = w.t().contiguous().to(ctx.device)            # tap by tap: (taps, channels)
 
     def forward(self, x: torch.Tensor, step, state: torch.Tensor) -> torch.Tensor:
         """``x`` (n, channels), row stride free; ``state`` (slots, >= state_floats) float32."""
