@@ -539,12 +539,57 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, int ldg, const floa
     }
 }
 
+// The same with 16-byte vectors: a thread makes Vec16<T>::N neighbouring outputs.
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_clamped_vec_kernel(const T* __restrict__ gu, int ldg, const float* __restrict__ bg, const float* __restrict__ bu,
+                       float limit, float alpha, float shift, T* __restrict__ out, int ldo, int F, size_t total_vecs) {
+    constexpr int N = Vec16<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_row = ldo / N;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vecs; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / per_row;
+        const int j = (int)(idx - r * per_row) * N;
+        float y[N];
+        if (j < F) {
+            float g[N], u[N];
+            Vec16<T>::load(gu + r * ldg + j, g);
+            Vec16<T>::load(gu + r * ldg + F + j, u);
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                float gv = g[e] + (bg != nullptr ? bg[j + e] : 0.f);
+                float uv = u[e] + (bu != nullptr ? bu[j + e] : 0.f);
+                if (limit > 0.f) {
+                    gv = fminf(gv, limit);
+                    uv = fminf(fmaxf(uv, -limit), limit);
+                }
+                y[e] = gv / (1.f + expf(-alpha * gv)) * (uv + shift);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < N; ++e) y[e] = (j + e == F) ? 1.f : 0.f;
+        }
+        Vec16<T>::store(out + r * ldo + j, y);
+    }
+}
+
 TIS_API int tis_glu_clamped(int dtype, const void* gu, int ldg, const float* bg, const float* bu, float limit,
                             float alpha, float shift, void* out, int ldo, int n, int F, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (F <= 0 || ldo < F || ldg < 2 * F) {
         tis_set_error("glu_clamped: %d columns, row lengths %d in and %d out", F, ldg, ldo);
         return TIS_BAD_SIZE;
+    }
+    const int per = dtype == TIS_BF16 ? 8 : 4;
+    if (F % per == 0 && ldg % per == 0 && ldo % per == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0) {
+        const size_t vecs = (size_t)n * (ldo / per);
+        size_t vblocks = (vecs + 255) / 256;
+        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        TIS_DISPATCH_DTYPE(dtype, T,
+            tis_launch(glu_clamped_vec_kernel<T>, dim3((unsigned)vblocks), dim3(256), 0, stream, (const T*)gu, ldg, bg, bu,
+                       limit, alpha, shift, (T*)out, ldo, F, vecs));
+        return tis_check_launch("glu_clamped");
     }
     const size_t total = (size_t)n * ldo;
     size_t blocks = (total + 255) / 256;

@@ -281,6 +281,81 @@ norm_mix_store_kernel(T* __restrict__ qkv, int ld, int nq, int nk, int nv, const
     }
 }
 
+// The same with 16-byte vectors, for widths and strides that are multiples of a vector.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_mix_store_vec_kernel(T* __restrict__ qkv, int ld, int nq, int nk, int nv, const float* __restrict__ wq,
+                          const float* __restrict__ wk, float eps, const T* __restrict__ v_other, int ld_other,
+                          const float* __restrict__ lambda, T* __restrict__ k_pages, size_t k_page_stride,
+                          size_t k_head_stride, T* __restrict__ v_pages, size_t v_page_stride, size_t v_head_stride,
+                          int kv_heads, int page_size, int num_pages, const int* __restrict__ block_table, int bt_stride,
+                          const int* __restrict__ positions, const int* __restrict__ row_slot, int* __restrict__ fault) {
+    constexpr int N = Vec16<T>::N;
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = positions[r];
+    const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
+    pdl_wait();
+    T* row = qkv + (size_t)r * ld;
+    float sq = 0.f, sk = 0.f;
+    float x[N];
+    if (wq != nullptr)
+        for (int i = threadIdx.x * N; i < nq; i += blockDim.x * N) {
+            Vec16<T>::load(row + i, x);
+#pragma unroll
+            for (int e = 0; e < N; ++e) sq = fmaf(x[e], x[e], sq);
+        }
+    if (wk != nullptr)
+        for (int i = threadIdx.x * N; i < nk; i += blockDim.x * N) {
+            Vec16<T>::load(row + nq + i, x);
+#pragma unroll
+            for (int e = 0; e < N; ++e) sk = fmaf(x[e], x[e], sk);
+        }
+    if (wq != nullptr) {
+        sq = block_sum(sq, red);
+        const float f = rsqrtf(sq / (float)nq + eps);
+        for (int i = threadIdx.x * N; i < nq; i += blockDim.x * N) {
+            Vec16<T>::load(row + i, x);
+#pragma unroll
+            for (int e = 0; e < N; ++e) x[e] = x[e] * f * wq[i + e];
+            Vec16<T>::store(row + i, x);
+        }
+    }
+    float fk = 1.f;
+    if (wk != nullptr) {
+        sk = block_sum(sk, red);
+        fk = rsqrtf(sk / (float)nk + eps);
+    }
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicExch(fault, 3);
+        return;
+    }
+    const int in_page = pos % page_size;
+    const int k_dim = nk / kv_heads, v_dim = nv / kv_heads;
+    for (int i = threadIdx.x * N; i < nk; i += blockDim.x * N) {
+        const int head = i / k_dim, e0 = i - head * k_dim;
+        Vec16<T>::load(row + nq + i, x);
+#pragma unroll
+        for (int e = 0; e < N; ++e) x[e] = x[e] * fk * (wk != nullptr ? wk[i + e] : 1.f);
+        Vec16<T>::store(k_pages + (size_t)page * k_page_stride + (size_t)head * k_head_stride + (size_t)in_page * k_dim + e0, x);
+    }
+    const float lam = (v_other != nullptr && lambda != nullptr) ? lambda[0] : 0.f;
+    for (int i = threadIdx.x * N; i < nv; i += blockDim.x * N) {
+        const int head = i / v_dim, e0 = i - head * v_dim;
+        Vec16<T>::load(row + nq + nk + i, x);
+        if (v_other != nullptr) {
+            float y[N];
+            Vec16<T>::load(v_other + (size_t)r * ld_other + i, y);
+#pragma unroll
+            for (int e = 0; e < N; ++e) x[e] = (1.f - lam) * x[e] + lam * y[e];
+        }
+        Vec16<T>::store(v_pages + (size_t)page * v_page_stride + (size_t)head * v_head_stride + (size_t)in_page * v_dim + e0, x);
+    }
+}
+
 TIS_API int tis_norm_mix_store(int dtype, void* qkv, int ld, int nq, int nk, int nv, const float* wq, const float* wk,
                                float eps, const void* v_other, int ld_other, const float* lambda, void* k_pages,
                                size_t k_page_stride, size_t k_head_stride, void* v_pages, size_t v_page_stride,
@@ -292,6 +367,18 @@ TIS_API int tis_norm_mix_store(int dtype, void* qkv, int ld, int nq, int nk, int
         tis_set_error("norm_mix_store: %d key and %d value elements for %d kv heads, page size %d", nk, nv, kv_heads,
                       page_size);
         return TIS_BAD_SIZE;
+    }
+    const int per = dtype == TIS_BF16 ? 8 : 4;
+    const int kd = nk / kv_heads, vd = nv / kv_heads;
+    if (nq % per == 0 && kd % per == 0 && vd % per == 0 && ld % per == 0 && (v_other == nullptr || ld_other % per == 0) &&
+        k_page_stride % per == 0 && k_head_stride % per == 0 && v_page_stride % per == 0 && v_head_stride % per == 0 &&
+        ((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)v_other) % 16 == 0) {
+        TIS_DISPATCH_DTYPE(dtype, T,
+            tis_launch(norm_mix_store_vec_kernel<T>, dim3(n), dim3(256), 0, stream, (T*)qkv, ld, nq, nk, nv, wq, wk, eps,
+                       (const T*)v_other, ld_other, lambda, (T*)k_pages, k_page_stride, k_head_stride, (T*)v_pages,
+                       v_page_stride, v_head_stride, kv_heads, page_size, num_pages, block_table, bt_stride, positions,
+                       row_slot, fault));
+        return tis_check_launch("norm_mix_store");
     }
     TIS_DISPATCH_DTYPE(dtype, T,
         tis_launch(norm_mix_store_kernel<T>, dim3(n), dim3(256), 0, stream, (T*)qkv, ld, nq, nk, nv, wq, wk, eps,
@@ -609,7 +696,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     if (r0 > 0 && row_slot[r0 - 1] == slot) return;
     const int rows = row_last[r0] - r0 + 1;
     const int kvh = head / (H / G);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int col = tid >> 2, part = tid & 3;
     const float decay_rate = expf(A_log[head]);
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
@@ -619,31 +706,57 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     for (int i = 0; i < D4; ++i) S[i] = S_glob[(size_t)(part * D4 + i) * v_dim];
     const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = 2 * G * KDIM + head * v_dim + col0;
     const int nv = H * v_dim;
+    // Preparing a chunk: eight threads a token, each with KDIM / 8 neighbouring key channels and four value columns.
+    // The raw values of the next chunk are loaded into registers before the current chunk is walked, so that their
+    // way from memory is hidden behind the recurrence.
+    constexpr int CH = KDIM / 8;
+    const int pt = tid >> 3, sub = tid & 7;
+    float rq[CH], rk[CH], ra[CH], rv[4], rb = 0.f;
+    auto fetch = [&](int c0) {
+        const bool live = c0 + pt < rows;
+        const size_t rr = (size_t)(r0 + c0 + pt);
+        const T* row = qkv + rr * ld;
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            rq[i] = live ? to_f32(row[q_off + sub * CH + i]) : 0.f;
+            rk[i] = live ? to_f32(row[k_off + sub * CH + i]) : 0.f;
+            ra[i] = live ? to_f32(a_in[rr * lda + head * KDIM + sub * CH + i]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rv[i] = live ? to_f32(row[v_off + sub * 4 + i]) : 0.f;
+        rb = (live && sub == 0) ? to_f32(b_in[rr * ldb + head]) : 0.f;
+    };
+    float bias[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) bias[i] = dt_bias[head * KDIM + sub * CH + i];
+    fetch(0);
     for (int c0 = 0; c0 < rows; c0 += DELTA_CHUNK) {
         const int cnt = min(DELTA_CHUNK, rows - c0);
-        __syncthreads();
-        for (int t = warp; t < cnt; t += 4) {
-            const T* row = qkv + (size_t)(r0 + c0 + t) * ld;
+        __syncthreads();                                // the chunk before is done with the shared arrays
+        {
             float sq = 0.f, sk = 0.f;
-            for (int i = lane; i < KDIM; i += 32) {
-                const float qv = to_f32(row[q_off + i]), kv = to_f32(row[k_off + i]);
-                sq += qv * qv;
-                sk += kv * kv;
+#pragma unroll
+            for (int i = 0; i < CH; ++i) { sq = fmaf(rq[i], rq[i], sq); sk = fmaf(rk[i], rk[i], sk); }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
             }
-            sq = warp_sum(sq);
-            sk = warp_sum(sk);
             const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.f / sqrtf(sk + unit_eps);
-            for (int i = lane; i < KDIM; i += 32) {
-                const int at = i + (i / D4) * 4;
-                qs[t][at] = to_f32(row[q_off + i]) * fq;
-                ks[t][at] = to_f32(row[k_off + i]) * fk;
-                const float a = to_f32(a_in[(size_t)(r0 + c0 + t) * lda + head * KDIM + i]) + dt_bias[head * KDIM + i];
-                gs[t][at] = expf(-decay_rate * softplus_f(a));
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+                const int ch = sub * CH + i;
+                const int at = ch + (ch / D4) * 4;
+                qs[pt][at] = rq[i] * fq;
+                ks[pt][at] = rk[i] * fk;
+                gs[pt][at] = expf(-decay_rate * softplus_f(ra[i] + bias[i]));
             }
-            vs[t][lane] = to_f32(row[v_off + lane]);
-            if (lane == 0) betas[t] = 1.f / (1.f + expf(-to_f32(b_in[(size_t)(r0 + c0 + t) * ldb + head])));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) vs[pt][sub * 4 + i] = rv[i];
+            if (sub == 0) betas[pt] = 1.f / (1.f + expf(-rb));
         }
         __syncthreads();
+        if (c0 + DELTA_CHUNK < rows) fetch(c0 + DELTA_CHUNK);
         for (int t = 0; t < cnt; ++t) {
             const float4* kt = reinterpret_cast<const float4*>(&ks[t][part * QP]);
             const float4* qt = reinterpret_cast<const float4*>(&qs[t][part * QP]);

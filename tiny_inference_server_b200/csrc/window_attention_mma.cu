@@ -8,7 +8,8 @@
 // warps owns 16 packed rows and walks all keys the tile can see, 64 at a time, with the running maximum and sum of
 // its rows in registers.  Tiles of at most 16 packed rows (decode rows): the four warps share the rows and take
 // every fourth tile of keys each; their partial results are merged through shared memory.  Key and value rows are
-// copied from their pages by cp.async, two tiles in flight.  Scores, bias, maximum, sum and the output are 32-bit;
+// copied from their pages by cp.async, two tiles in flight.  The key tiles of decode rows may also be shared out over
+// several CTAs (grid.z), whose partial results a second small kernel merges.  Scores, bias, maximum, sum and the output are 32-bit;
 // the probabilities enter the second product rounded to bfloat16.
 #include "common.cuh"
 
@@ -66,6 +67,7 @@ struct Params {
     float scale;
     const float* r1; const float* r2;
     int* fault;
+    float* partial;          // [tiles][G][splits][16][VD + 2]: unnormalised out, maximum, sum (key splits over CTAs)
 };
 
 // Copies the key and value rows first .. first + 63 (those that exist: j <= last) of a request into a stage.  Two
@@ -120,7 +122,18 @@ window_attention_mma_kernel(const Params p) {
     if (tid == 0) bad = 0;
     const int last = pos0 + nrows - 1;                         // the last key any row of the tile sees
     const int first = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int ntiles = (last - first) / KEYS + 1;
+    int ntiles = (last - first) / KEYS + 1;
+    int kt_begin = 0;
+    const int splits = gridDim.z;
+    if (splits > 1) {
+        // the key tiles of a decode row's tile are shared out over the CTAs of grid.z; any other tile is one CTA's
+        if (!split_keys) { if (blockIdx.z > 0) return; }
+        else {
+            const int per = (ntiles + splits - 1) / splits;
+            kt_begin = min(ntiles, (int)blockIdx.z * per);
+            ntiles = min(ntiles, kt_begin + per);
+        }
+    }
     const int base = split_keys ? 0 : warp * 16;               // first packed row of this warp
     // this thread's two packed rows: base + g and base + g + 8
     const int m_a = base + g, m_b = m_a + 8;
@@ -141,7 +154,7 @@ window_attention_mma_kernel(const Params p) {
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();                                           // `bad` is initialised before any load may set it
-    load_tile(p, slot, kvh, first, last, kbuf, vbuf, &bad);
+    if (kt_begin < ntiles) load_tile(p, slot, kvh, first + kt_begin * KEYS, last, kbuf, vbuf, &bad);
     cp_async_commit();
     float o[VD / 8][4];
 #pragma unroll
@@ -150,14 +163,14 @@ window_attention_mma_kernel(const Params p) {
     unsigned qf[KD / 16][4];
     // positions of the first and last row among this warp's packed rows
     const int w_lo = pos0 + base / gq, w_hi = min(pos0 + (base + 15) / gq, last);
-    for (int kt = 0; kt < ntiles; ++kt) {
-        const int stage = kt & 1;
+    for (int kt = kt_begin; kt < ntiles; ++kt) {
+        const int stage = (kt - kt_begin) & 1;
         if (kt + 1 < ntiles)
             load_tile(p, slot, kvh, first + (kt + 1) * KEYS, last, kbuf + (stage ^ 1) * KEYS * KS, vbuf + (stage ^ 1) * KEYS * VS, &bad);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (kt == 0) {
+        if (kt == kt_begin) {
 #pragma unroll
             for (int kk = 0; kk < KD / 16; ++kk)
                 ldmatrix_x4(qf[kk], qs + (base + (lane & 7) + 8 * ((lane >> 3) & 1)) * QS + kk * 16 + 8 * (lane >> 4));
@@ -278,6 +291,12 @@ window_attention_mma_kernel(const Params p) {
                 num = fmaf(src[c], f, num);
                 den = fmaf(src[VD + 1], f, den);
             }
+            if (splits > 1) {                                  // this CTA's share of the keys: left for the merge kernel
+                float* dst = p.partial + ((((size_t)tile * p.G + kvh) * splits + blockIdx.z) * 16 + mrow) * PS;
+                dst[c] = num;
+                if (c == 0) { dst[VD] = mm; dst[VD + 1] = den; }
+                continue;
+            }
             float x = den > 0.f ? num / den : 0.f;
             const size_t row = (size_t)(row0 + mrow / gq);
             const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
@@ -307,7 +326,43 @@ window_attention_mma_kernel(const Params p) {
     }
 }
 
+// The key splits of decode tiles, merged: a CTA per (tile, kv head), a thread per output element.
+__global__ void __launch_bounds__(128)
+window_attention_merge_kernel(const Params p, int splits) {
+    pdl_launch_dependents();
+    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
+    const int gq = p.H / p.G;
+    const int packed = nrows * gq;
+    if (nrows <= 0 || p.row_slot[row0] < 0 || packed > 16) return;      // tiles of many rows were one CTA's
+    pdl_wait();
+    constexpr int PS = VD + 2;
+    const float* part = p.partial + (((size_t)tile * p.G + kvh) * splits) * 16 * PS;
+    for (int idx = threadIdx.x; idx < packed * VD; idx += blockDim.x) {
+        const int mrow = idx / VD, c = idx - mrow * VD;
+        float mm = -INFINITY;
+        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part[((size_t)s * 16 + mrow) * PS + VD]);
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float* src = part + ((size_t)s * 16 + mrow) * PS;
+            const float f = src[VD] == -INFINITY ? 0.f : __expf(src[VD] - mm);
+            num = fmaf(src[c], f, num);
+            den = fmaf(src[VD + 1], f, den);
+        }
+        float x = den > 0.f ? num / den : 0.f;
+        const size_t row = (size_t)(row0 + mrow / gq);
+        const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
+        if (p.gate != nullptr) x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + col])));
+        p.out[row * p.ldo + col] = __float2bfloat16_rn(x);
+    }
+}
+
 }  // namespace
+
+// Floats of scratch that `splits` key splits of `num_tiles` tiles need.
+TIS_API size_t tis_window_attention_partial_floats(int num_tiles, int G, int splits) {
+    return (size_t)num_tiles * G * splits * 16 * (VD + 2);
+}
 
 TIS_API int tis_window_attention_mma_dims(int* kd, int* vd) {
     *kd = KD;
@@ -323,8 +378,12 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
                                      const int* block_table, int bt_stride, int num_pages, const int* positions,
                                      const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
                                      int H, int G, int page_size, int window, float scale, const float* r1,
-                                     const float* r2, int* fault, cudaStream_t stream) {
+                                     const float* r2, int splits, float* partial, int* fault, cudaStream_t stream) {
     if (num_tiles <= 0) return TIS_OK;
+    if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) {
+        tis_set_error("window_attention_mma: %d key splits%s", splits, splits > 1 ? " without scratch" : "");
+        return TIS_BAD_SIZE;
+    }
     if (H <= 0 || G <= 0 || H % G || H / G > ROWS || page_size <= 0 || window < 0 || ldq % 8 || ldg % 2 || ldo % 2 ||
         k_page_stride % 8 || k_head_stride % 8 || v_page_stride % 8 || v_head_stride % 8 ||
         ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 || ((uintptr_t)gate | (uintptr_t)out) % 4) {
@@ -340,13 +399,16 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
     p.v_pages = (const bf16*)v_pages; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride;
     p.block_table = block_table; p.bt_stride = bt_stride; p.num_pages = num_pages;
     p.positions = positions; p.row_slot = row_slot; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
-    p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.scale = scale; p.r1 = r1; p.r2 = r2; p.fault = fault;
+    p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.scale = scale; p.r1 = r1; p.r2 = r2; p.fault = fault; p.partial = partial;
     const size_t smem = sizeof(bf16) * ((size_t)ROWS * QS + 2 * KEYS * KS + 2 * KEYS * VS);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
         cudaFuncSetAttribute(window_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_set = true;
     }
-    tis_launch(window_attention_mma_kernel, dim3(num_tiles, G), dim3(THREADS), smem, stream, p);
-    return tis_check_launch("window_attention_mma");
+    tis_launch(window_attention_mma_kernel, dim3(num_tiles, G, splits), dim3(THREADS), smem, stream, p);
+    int st = tis_check_launch("window_attention_mma");
+    if (st != TIS_OK || splits == 1) return st;
+    tis_launch(window_attention_merge_kernel, dim3(num_tiles, G), dim3(128), 0, stream, p, splits);
+    return tis_check_launch("window_attention_merge");
 }

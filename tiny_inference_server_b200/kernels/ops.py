@@ -850,6 +850,8 @@ def window_attention_library(k_dim: int, v_dim: int):
 #: bfloat16 steps run windowed attention on the tensor cores;
 #: TIS_WINDOW_ATTENTION_MMA=0 keeps every step on the CUDA-core kernel
 WINDOW_ATTENTION_MMA = os.environ.get("TIS_WINDOW_ATTENTION_MMA", "1") != "0"
+#: CTAs that the key splits of a decode step's tiles aim at (two per SM)
+WINDOW_ATTENTION_CTAS = 2 * 148
 
 
 def window_attention_mma_usable(q: torch.Tensor, gate, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor) -> bool:
@@ -885,12 +887,25 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
         row0, rows, count = step.plan(window_plan.planner(num_heads // kv_heads))
         wlib = window_attention_library(k_dim, v_dim)
         calls["window_attention_mma"] += 1
+        # a decode step has few tiles, each with many keys to walk: share the keys of a tile out over several CTAs
+        # (about two CTAs per SM in all), whose partial results a second launch merges
+        splits, partial = 1, None
+        if getattr(step, "decode_only", False) and count > 0:
+            keys = step.max_position + 1 if not window else min(int(window), step.max_position + 1)
+            key_tiles = keys // 64 + 1
+            splits = max(1, min(key_tiles, WINDOW_ATTENTION_CTAS // max(1, count * kv_heads), 64))
+            if splits > 1:
+                wlib.tis_window_attention_partial_floats.restype = ctypes.c_size_t
+                partial = torch.empty(wlib.tis_window_attention_partial_floats(count, kv_heads, splits), dtype=torch.float32,
+                                      device=q.device)
+                global launches
+                launches += 1
         _check(wlib.tis_window_attention_mma(_p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                              _p(out), out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs,
                                              _p(block_table), block_table.stride(0), k_pages.shape[0], _p(positions),
                                              _p(row_slot), _p(row0), _p(rows), count, num_heads, kv_heads, page_size,
-                                             int(window or 0), _f(scale), _p(bias_slope), _p(bias_rate), _p(fault),
-                                             _stream()), wlib)
+                                             int(window or 0), _f(scale), _p(bias_slope), _p(bias_rate), splits, _p(partial),
+                                             _p(fault), _stream()), wlib)
         return out
     calls["window_attention"] += 1
     _check(lib.tis_window_attention(_dt(q), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
