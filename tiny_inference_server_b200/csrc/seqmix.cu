@@ -672,18 +672,24 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
     }
 }
 
-// The same recurrence with more parallelism, for value widths that are multiples of 32 and key widths 4 * D4: a CTA
-// takes 32 columns of one head's state, four lanes share a column (lane p keeps the key channels p * D4 .. + D4 - 1 of
-// it in registers) and add their partial sums with two shuffles.  The chunk's q^, k^ and g lie in shared memory with
-// four floats of padding after every quarter, so that the four lanes of a column read different banks with 16-byte
-// loads.  The outputs leave unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
-template <typename T, int D4>
-__global__ void __launch_bounds__(128)
+// The same recurrence with more parallelism, for key widths LANES * DL and value widths that are multiples of the
+// columns a CTA takes: LANES lanes share a column of one head's state (lane p keeps the key channels p * DL .. + DL - 1
+// of it in registers) and add their partial sums with shuffles; a CTA takes COLS = 32 columns with four lanes each, or
+// 64 columns with eight lanes each (sixteen warps, so that a scheduler has four recurrences to switch between).  The
+// chunk's q^, k^ and g lie in shared memory with four floats of padding after every lane's share, so that the lanes of
+// a column read different banks with 16-byte loads.  A chunk is prepared by all threads, NT / 16 to a token; the raw
+// values of the next chunk are loaded into registers before the current chunk is walked.  The outputs leave
+// unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
+template <typename T, int DL, int LANES>
+__global__ void __launch_bounds__(LANES == 8 ? 512 : 128)
 delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
                         int lda, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
                         float q_scale, float* __restrict__ state, size_t state_stride, float* __restrict__ o_raw,
                         const int* __restrict__ row_slot, const int* __restrict__ row_last, int H, int G, int v_dim) {
-    constexpr int KDIM = 4 * D4, QP = D4 + 4, ROW = 4 * QP, COLS = 32;
+    constexpr int KDIM = LANES * DL, QP = DL + 4, ROW = LANES * QP, COLS = LANES == 8 ? 64 : 32, NT = COLS * LANES;
+    constexpr int PT = NT / DELTA_CHUNK;                // threads that prepare a token
+    constexpr int CH = KDIM / PT, VPT = COLS / PT;      // key channels and value columns of each
+    static_assert(KDIM % PT == 0 && COLS % PT == 0 && DL % 2 == 0, "widths");
     __shared__ __align__(16) float qs[DELTA_CHUNK][ROW];
     __shared__ __align__(16) float ks[DELTA_CHUNK][ROW];
     __shared__ __align__(16) float gs[DELTA_CHUNK][ROW];
@@ -697,21 +703,17 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int rows = row_last[r0] - r0 + 1;
     const int kvh = head / (H / G);
     const int tid = threadIdx.x;
-    const int col = tid >> 2, part = tid & 3;
+    const int col = tid / LANES, part = tid % LANES;
     const float decay_rate = expf(A_log[head]);
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
-    float S[D4];
+    float S[DL];
     pdl_wait();
 #pragma unroll
-    for (int i = 0; i < D4; ++i) S[i] = S_glob[(size_t)(part * D4 + i) * v_dim];
+    for (int i = 0; i < DL; ++i) S[i] = S_glob[(size_t)(part * DL + i) * v_dim];
     const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = 2 * G * KDIM + head * v_dim + col0;
     const int nv = H * v_dim;
-    // Preparing a chunk: eight threads a token, each with KDIM / 8 neighbouring key channels and four value columns.
-    // The raw values of the next chunk are loaded into registers before the current chunk is walked, so that their
-    // way from memory is hidden behind the recurrence.
-    constexpr int CH = KDIM / 8;
-    const int pt = tid >> 3, sub = tid & 7;
-    float rq[CH], rk[CH], ra[CH], rv[4], rb = 0.f;
+    const int pt = tid / PT, sub = tid % PT;
+    float rq[CH], rk[CH], ra[CH], rv[VPT], rb = 0.f;
     auto fetch = [&](int c0) {
         const bool live = c0 + pt < rows;
         const size_t rr = (size_t)(r0 + c0 + pt);
@@ -723,7 +725,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             ra[i] = live ? to_f32(a_in[rr * lda + head * KDIM + sub * CH + i]) : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) rv[i] = live ? to_f32(row[v_off + sub * 4 + i]) : 0.f;
+        for (int i = 0; i < VPT; ++i) rv[i] = live ? to_f32(row[v_off + sub * VPT + i]) : 0.f;
         rb = (live && sub == 0) ? to_f32(b_in[rr * ldb + head]) : 0.f;
     };
     float bias[CH];
@@ -738,7 +740,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
 #pragma unroll
             for (int i = 0; i < CH; ++i) { sq = fmaf(rq[i], rq[i], sq); sk = fmaf(rk[i], rk[i], sk); }
 #pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
+            for (int o = 1; o < PT; o <<= 1) {
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
                 sk += __shfl_xor_sync(0xffffffffu, sk, o);
             }
@@ -746,50 +748,47 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
 #pragma unroll
             for (int i = 0; i < CH; ++i) {
                 const int ch = sub * CH + i;
-                const int at = ch + (ch / D4) * 4;
+                const int at = ch + (ch / DL) * 4;
                 qs[pt][at] = rq[i] * fq;
                 ks[pt][at] = rk[i] * fk;
                 gs[pt][at] = expf(-decay_rate * softplus_f(ra[i] + bias[i]));
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) vs[pt][sub * 4 + i] = rv[i];
+            for (int i = 0; i < VPT; ++i) vs[pt][sub * VPT + i] = rv[i];
             if (sub == 0) betas[pt] = 1.f / (1.f + expf(-rb));
         }
         __syncthreads();
         if (c0 + DELTA_CHUNK < rows) fetch(c0 + DELTA_CHUNK);
         for (int t = 0; t < cnt; ++t) {
-            const float4* kt = reinterpret_cast<const float4*>(&ks[t][part * QP]);
-            const float4* qt = reinterpret_cast<const float4*>(&qs[t][part * QP]);
-            const float4* gt = reinterpret_cast<const float4*>(&gs[t][part * QP]);
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            const float2* kt = reinterpret_cast<const float2*>(&ks[t][part * QP]);
+            const float2* qt = reinterpret_cast<const float2*>(&qs[t][part * QP]);
+            const float2* gt = reinterpret_cast<const float2*>(&gs[t][part * QP]);
+            float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < D4 / 4; ++i) {
-                const float4 gv = gt[i], kv = kt[i];
-                S[4 * i] *= gv.x; S[4 * i + 1] *= gv.y; S[4 * i + 2] *= gv.z; S[4 * i + 3] *= gv.w;
-                d0 = fmaf(S[4 * i], kv.x, d0); d1 = fmaf(S[4 * i + 1], kv.y, d1);
-                d2 = fmaf(S[4 * i + 2], kv.z, d2); d3 = fmaf(S[4 * i + 3], kv.w, d3);
+            for (int i = 0; i < DL / 2; ++i) {
+                const float2 gv = gt[i], kv = kt[i];
+                S[2 * i] *= gv.x; S[2 * i + 1] *= gv.y;
+                d0 = fmaf(S[2 * i], kv.x, d0); d1 = fmaf(S[2 * i + 1], kv.y, d1);
             }
-            float dot = (d0 + d1) + (d2 + d3);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            float dot = d0 + d1;
+#pragma unroll
+            for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
             const float u = betas[t] * (vs[t][col] - dot);
-            d0 = d1 = d2 = d3 = 0.f;
+            d0 = d1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < D4 / 4; ++i) {
-                const float4 kv = kt[i], qv = qt[i];
-                S[4 * i] = fmaf(kv.x, u, S[4 * i]); S[4 * i + 1] = fmaf(kv.y, u, S[4 * i + 1]);
-                S[4 * i + 2] = fmaf(kv.z, u, S[4 * i + 2]); S[4 * i + 3] = fmaf(kv.w, u, S[4 * i + 3]);
-                d0 = fmaf(S[4 * i], qv.x, d0); d1 = fmaf(S[4 * i + 1], qv.y, d1);
-                d2 = fmaf(S[4 * i + 2], qv.z, d2); d3 = fmaf(S[4 * i + 3], qv.w, d3);
+            for (int i = 0; i < DL / 2; ++i) {
+                const float2 kv = kt[i], qv = qt[i];
+                S[2 * i] = fmaf(kv.x, u, S[2 * i]); S[2 * i + 1] = fmaf(kv.y, u, S[2 * i + 1]);
+                d0 = fmaf(S[2 * i], qv.x, d0); d1 = fmaf(S[2 * i + 1], qv.y, d1);
             }
-            float o = (d0 + d1) + (d2 + d3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            float o = d0 + d1;
+#pragma unroll
+            for (int sh = 1; sh < LANES; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
             if (part == 0) o_raw[(size_t)(r0 + c0 + t) * nv + head * v_dim + col0 + col] = o;
         }
     }
 #pragma unroll
-    for (int i = 0; i < D4; ++i) S_glob[(size_t)(part * D4 + i) * v_dim] = S[i];
+    for (int i = 0; i < DL; ++i) S_glob[(size_t)(part * DL + i) * v_dim] = S[i];
 }
 
 // out[r, head, :] = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate) for every (row, head): a warp each.
@@ -815,13 +814,14 @@ delta_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gat
     }
 }
 
-template <typename T, int D4>
+template <typename T, int DL, int LANES>
 static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb, const T* a_in, int lda, const T* gate, int ldg,
                                    const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
                                    float q_scale, float* state, size_t state_stride, T* out, int ldo, float* o_raw,
                                    const int* row_slot, const int* row_last, int n, int H, int G, int v_dim,
                                    cudaStream_t stream) {
-    tis_launch(delta_rule_split_kernel<T, D4>, dim3(n, H, v_dim / 32), dim3(128), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
+    constexpr int COLS = LANES == 8 ? 64 : 32;
+    tis_launch(delta_rule_split_kernel<T, DL, LANES>, dim3(n, H, v_dim / COLS), dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
                dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, H, G, v_dim);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK) return st;
@@ -864,21 +864,23 @@ TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in,
                            int k_dim, int v_dim, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (o_raw != nullptr && H > 0 && G > 0 && H % G == 0 && tis_delta_rule_splits(k_dim, v_dim)) {
-#define TIS_DELTA_SPLIT(D)                                                                                             \
-    case 4 * D:                                                                                                        \
-        TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule_split<T, D>((const T*)qkv, ld, (const T*)b_in, ldb,      \
-            (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state,           \
-            state_stride, (T*)out, ldo, o_raw, row_slot, row_last, n, H, G, v_dim, stream));                           \
-        break;
-        switch (k_dim) {
-            TIS_DELTA_SPLIT(4)
-            TIS_DELTA_SPLIT(8)
-            TIS_DELTA_SPLIT(12)
-            TIS_DELTA_SPLIT(16)
-            TIS_DELTA_SPLIT(24)
-            TIS_DELTA_SPLIT(32)
-            default: break;
+#define TIS_DELTA_SPLIT(K, DL, LANES)                                                                                 \
+    if (k_dim == K)                                                                                                    \
+        TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule_split<T, DL, LANES>((const T*)qkv, ld, (const T*)b_in,   \
+            ldb, (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state,      \
+            state_stride, (T*)out, ldo, o_raw, row_slot, row_last, n, H, G, v_dim, stream));
+        if (v_dim % 64 == 0) {                          // eight lanes a column, 64 columns a CTA
+            TIS_DELTA_SPLIT(32, 4, 8)
+            TIS_DELTA_SPLIT(64, 8, 8)
+            TIS_DELTA_SPLIT(96, 12, 8)
+            TIS_DELTA_SPLIT(128, 16, 8)
         }
+        TIS_DELTA_SPLIT(16, 4, 4)
+        TIS_DELTA_SPLIT(32, 8, 4)
+        TIS_DELTA_SPLIT(48, 12, 4)
+        TIS_DELTA_SPLIT(64, 16, 4)
+        TIS_DELTA_SPLIT(96, 24, 4)
+        TIS_DELTA_SPLIT(128, 32, 4)
 #undef TIS_DELTA_SPLIT
     }
     if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > 256) {

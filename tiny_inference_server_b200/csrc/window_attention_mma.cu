@@ -24,7 +24,8 @@ namespace {
 
 constexpr int KD = TIS_KD, VD = TIS_VD;
 static_assert(KD % 16 == 0 && VD % 16 == 0, "key width and value width must be multiples of 16");
-constexpr int ROWS = 64, KEYS = 64, THREADS = 128;
+constexpr int ROWS = 64, KEYS = 64, THREADS = 128;       // ROWS == KEYS: the queries fit a key stage
+constexpr int MIN_CTAS = KD + VD <= 256 ? 3 : 1;          // CTAs an SM that the register budget is set for
 constexpr int QS = KD + 8, KS = KD + 8, VS = VD + 8;       // row strides in shared memory (elements): no bank conflicts
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
@@ -101,13 +102,13 @@ __device__ __forceinline__ void load_tile(const Params& p, int slot, int kvh, in
     }
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
 window_attention_mma_kernel(const Params p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int bad;
-    bf16* qs = reinterpret_cast<bf16*>(smem_raw);              // [ROWS][QS]
-    bf16* kbuf = qs + ROWS * QS;                               // [2][KEYS][KS]
+    bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);            // [2][KEYS][KS]
     bf16* vbuf = kbuf + 2 * KEYS * KS;                         // [2][KEYS][VS]
+    bf16* qs = kbuf + KEYS * KS;                               // [ROWS][QS]: the queries pass through the second key stage
     pdl_launch_dependents();
     const int tile = blockIdx.x, kvh = blockIdx.y;
     const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
@@ -156,11 +157,17 @@ window_attention_mma_kernel(const Params p) {
     __syncthreads();                                           // `bad` is initialised before any load may set it
     if (kt_begin < ntiles) load_tile(p, slot, kvh, first + kt_begin * KEYS, last, kbuf, vbuf, &bad);
     cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    unsigned qf[KD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < KD / 16; ++kk)
+        ldmatrix_x4(qf[kk], qs + (base + (lane & 7) + 8 * ((lane >> 3) & 1)) * QS + kk * 16 + 8 * (lane >> 4));
+    __syncthreads();                                           // the queries are in registers: the stage is free
     float o[VD / 8][4];
 #pragma unroll
     for (int n = 0; n < VD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    unsigned qf[KD / 16][4];
     // positions of the first and last row among this warp's packed rows
     const int w_lo = pos0 + base / gq, w_hi = min(pos0 + (base + 15) / gq, last);
     for (int kt = kt_begin; kt < ntiles; ++kt) {
@@ -170,11 +177,6 @@ window_attention_mma_kernel(const Params p) {
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (kt == kt_begin) {
-#pragma unroll
-            for (int kk = 0; kk < KD / 16; ++kk)
-                ldmatrix_x4(qf[kk], qs + (base + (lane & 7) + 8 * ((lane >> 3) & 1)) * QS + kk * 16 + 8 * (lane >> 4));
-        }
         const bf16* ks = kbuf + stage * KEYS * KS;
         const bf16* vs = vbuf + stage * KEYS * VS;
         const int j0 = first + kt * KEYS;
@@ -195,19 +197,35 @@ window_attention_mma_kernel(const Params p) {
                     mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
                 }
             }
-            // scale, bias, mask; the maximum of each row over the tile
+            // scale, bias, mask; the maximum of each row over the tile.  A tile that every row of the warp sees
+            // whole (the usual case inside a window) needs no mask.
+            const bool whole = base + 15 < packed && j0 + KEYS - 1 <= w_lo && (p.window <= 0 || j0 > w_hi - p.window);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (whole) {
 #pragma unroll
-            for (int n = 0; n < KEYS / 8; ++n) {
+                for (int n = 0; n < KEYS / 8; ++n) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = j0 + n * 8 + 2 * t4 + (e & 1);
-                    const int pos = (e & 2) ? pos_b : pos_a;
-                    const bool ok = ((e & 2) ? row_b : row_a) && j <= pos && (p.window <= 0 || j > pos - p.window);
-                    float v = -INFINITY;
-                    if (ok) v = s[n][e] * p.scale - ((e & 2) ? b1_b : b1_a) * __logf(fmaf((e & 2) ? b2_b : b2_a, (float)(pos - j), 1.f));
-                    s[n][e] = v;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = j0 + n * 8 + 2 * t4 + (e & 1);
+                        const int pos = (e & 2) ? pos_b : pos_a;
+                        const float v = s[n][e] * p.scale - ((e & 2) ? b1_b : b1_a) * __logf(fmaf((e & 2) ? b2_b : b2_a, (float)(pos - j), 1.f));
+                        s[n][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = j0 + n * 8 + 2 * t4 + (e & 1);
+                        const int pos = (e & 2) ? pos_b : pos_a;
+                        const bool ok = ((e & 2) ? row_b : row_a) && j <= pos && (p.window <= 0 || j > pos - p.window);
+                        float v = -INFINITY;
+                        if (ok) v = s[n][e] * p.scale - ((e & 2) ? b1_b : b1_a) * __logf(fmaf((e & 2) ? b2_b : b2_a, (float)(pos - j), 1.f));
+                        s[n][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
                 }
             }
             float corr[2];
@@ -400,7 +418,7 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
     p.block_table = block_table; p.bt_stride = bt_stride; p.num_pages = num_pages;
     p.positions = positions; p.row_slot = row_slot; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
     p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.scale = scale; p.r1 = r1; p.r2 = r2; p.fault = fault; p.partial = partial;
-    const size_t smem = sizeof(bf16) * ((size_t)ROWS * QS + 2 * KEYS * KS + 2 * KEYS * VS);
+    const size_t smem = sizeof(bf16) * ((size_t)2 * KEYS * KS + 2 * KEYS * VS);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
         cudaFuncSetAttribute(window_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -31,7 +31,7 @@ from .engine.batch import StepEntry
 from .engine.runner import ModelRunner
 
 #: requests live at a time that a replay is sized for unless told otherwise
-MAX_LIVE = 8
+MAX_LIVE = 4
 
 
 class TraceReplayer:
