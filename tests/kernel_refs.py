@@ -186,7 +186,7 @@ def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row
 
 
 def delta_rule(qkv, beta, decay_in, gate, a_log, dt_bias, norm_weight, eps, unit_eps, q_scale, state, out, row_slot,
-               row_last, num_heads, qk_heads, k_dim, v_dim):
+               row_last, num_heads, qk_heads, k_dim, v_dim, requests=None, segments=None):
     H, G = num_heads, qk_heads
     nq = G * k_dim
     rate = torch.exp(a_log.to(torch.float32))[:, None]

@@ -509,7 +509,8 @@ def test_delta_rule_in_portions_and_far_memory(dtype, H, G, kd, vd):
         row_slot, row_last = _rows([n], [2])
         out = torch.empty(n, nv, dtype=DT[dtype], device="cuda")
         ops.delta_rule(qkv[rows].cuda(), beta[rows].cuda(), a[rows].cuda(), gate[rows].cuda(), a_log.cuda(), dt_bias.cuda(),
-                       norm_w.cuda(), eps, 1e-6, kd ** -0.5, state, out, row_slot, row_last, H, G, kd, vd)
+                       norm_w.cuda(), eps, 1e-6, kd ** -0.5, state, out, row_slot, row_last, H, G, kd, vd,
+                       requests=1 if i % 2 else None)     # few requests: the kernel with narrow column slices
         got[rows] = out
         fed += n
     _close(got, ref, 3e-2 if dtype == "bfloat16" else 1e-4, "delta rule")

@@ -535,7 +535,8 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
 //   S <- diag(g) S;  u = beta * (v - S^T k^);  S <- S + k^ u^T;  o = S^T q^
 //   out = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate)                                   (over v_dim)
 // A row of `qkv` holds the queries and keys of G heads (k_dim each) and the values of H heads (v_dim each).
-// One CTA per (request of the step, head); the CTAs of rows that are not the first of their request leave at once.
+// One CTA per (head, row); the CTAs of rows that are not the first of their request in the step leave at once (rows
+// are the slowest grid dimension, so that the CTAs with work are not queued behind thousands of those).
 // Every column of S is a recurrence of its own: a thread keeps one column (in registers when DIM > 0 is the key
 // width, else in shared memory).  Tokens are taken CHUNK at a time: all threads prepare q^, k^, g, beta and v of
 // the chunk, then every thread walks its column through the chunk without a barrier, then the outputs of the
@@ -555,7 +556,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                   int v_dim) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
-    const int r0 = blockIdx.x, head = blockIdx.y;
+    const int head = blockIdx.x, r0 = blockIdx.y;
     const int slot = row_slot[r0];
     if (slot < 0) return;
     if (r0 > 0 && row_slot[r0 - 1] == slot) return;
@@ -674,19 +675,21 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
 
 // The same recurrence with more parallelism, for key widths LANES * DL and value widths that are multiples of the
 // columns a CTA takes: LANES lanes share a column of one head's state (lane p keeps the key channels p * DL .. + DL - 1
-// of it in registers) and add their partial sums with shuffles; a CTA takes COLS = 32 columns with four lanes each, or
-// 64 columns with eight lanes each (sixteen warps, so that a scheduler has four recurrences to switch between).  The
+// of it in registers) and add their partial sums with shuffles; a CTA takes COLS columns: 32 with four lanes each, or,
+// with eight lanes each, 64 (sixteen warps: a scheduler has four recurrences to switch between) or 16 (four times the
+// CTAs, for steps of few requests, where a head's columns are all the parallelism there is).  The
 // chunk's q^, k^ and g lie in shared memory with four floats of padding after every lane's share, so that the lanes of
 // a column read different banks with 16-byte loads.  A chunk is prepared by all threads, NT / 16 to a token; the raw
 // values of the next chunk are loaded into registers before the current chunk is walked.  The outputs leave
 // unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
-template <typename T, int DL, int LANES>
-__global__ void __launch_bounds__(LANES == 8 ? 512 : 128)
+template <typename T, int DL, int LANES, int COLS>
+__global__ void __launch_bounds__(COLS * LANES)
 delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
                         int lda, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
                         float q_scale, float* __restrict__ state, size_t state_stride, float* __restrict__ o_raw,
-                        const int* __restrict__ row_slot, const int* __restrict__ row_last, int H, int G, int v_dim) {
-    constexpr int KDIM = LANES * DL, QP = DL + 4, ROW = LANES * QP, COLS = LANES == 8 ? 64 : 32, NT = COLS * LANES;
+                        const int* __restrict__ row_slot, const int* __restrict__ row_last,
+                        const int* __restrict__ seg_row0, int H, int G, int v_dim) {
+    constexpr int KDIM = LANES * DL, QP = DL + 4, ROW = LANES * QP, NT = COLS * LANES;
     constexpr int PT = NT / DELTA_CHUNK;                // threads that prepare a token
     constexpr int CH = KDIM / PT, VPT = COLS / PT;      // key channels and value columns of each
     static_assert(KDIM % PT == 0 && COLS % PT == 0 && DL % 2 == 0, "widths");
@@ -696,7 +699,10 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     __shared__ float vs[DELTA_CHUNK][COLS];
     __shared__ float betas[DELTA_CHUNK];
     pdl_launch_dependents();
-    const int r0 = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
+    const int head = blockIdx.x, col0 = blockIdx.y * COLS;
+    // grid.z: the requests of the step, by their first rows (`seg_row0`), or, without that list, every row (the CTAs
+    // of rows that are not the first of their request leave at once)
+    const int r0 = seg_row0 != nullptr ? seg_row0[blockIdx.z] : (int)blockIdx.z;
     const int slot = row_slot[r0];
     if (slot < 0) return;
     if (r0 > 0 && row_slot[r0 - 1] == slot) return;
@@ -759,27 +765,56 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
         }
         __syncthreads();
         if (c0 + DELTA_CHUNK < rows) fetch(c0 + DELTA_CHUNK);
+        // With registers to spare (the narrow CTAs) a token's vectors are read from shared memory while the token
+        // before is walked, so that the recurrence never waits for them.
+        constexpr bool AHEAD = NT <= 128 && LANES == 8;
+        float2 kn[AHEAD ? DL / 2 : 1], qn[AHEAD ? DL / 2 : 1], gn[AHEAD ? DL / 2 : 1];
+        float vn = 0.f, bn = 0.f;
+        auto ahead = [&](int t) {
+            if (AHEAD) {
+                const float2* kt = reinterpret_cast<const float2*>(&ks[t][part * QP]);
+                const float2* qt = reinterpret_cast<const float2*>(&qs[t][part * QP]);
+                const float2* gt = reinterpret_cast<const float2*>(&gs[t][part * QP]);
+#pragma unroll
+                for (int i = 0; i < DL / 2; ++i) { kn[i] = kt[i]; qn[i] = qt[i]; gn[i] = gt[i]; }
+                vn = vs[t][col];
+                bn = betas[t];
+            }
+        };
+        ahead(0);
         for (int t = 0; t < cnt; ++t) {
-            const float2* kt = reinterpret_cast<const float2*>(&ks[t][part * QP]);
-            const float2* qt = reinterpret_cast<const float2*>(&qs[t][part * QP]);
-            const float2* gt = reinterpret_cast<const float2*>(&gs[t][part * QP]);
+            float2 kc[DL / 2], qc[DL / 2], gc[DL / 2];
+            float vc, bc;
+            if (AHEAD) {
+#pragma unroll
+                for (int i = 0; i < DL / 2; ++i) { kc[i] = kn[i]; qc[i] = qn[i]; gc[i] = gn[i]; }
+                vc = vn;
+                bc = bn;
+                if (t + 1 < cnt) ahead(t + 1);
+            } else {
+                const float2* kt = reinterpret_cast<const float2*>(&ks[t][part * QP]);
+                const float2* qt = reinterpret_cast<const float2*>(&qs[t][part * QP]);
+                const float2* gt = reinterpret_cast<const float2*>(&gs[t][part * QP]);
+#pragma unroll
+                for (int i = 0; i < DL / 2; ++i) { kc[i] = kt[i]; qc[i] = qt[i]; gc[i] = gt[i]; }
+                vc = vs[t][col];
+                bc = betas[t];
+            }
             float d0 = 0.f, d1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DL / 2; ++i) {
-                const float2 gv = gt[i], kv = kt[i];
-                S[2 * i] *= gv.x; S[2 * i + 1] *= gv.y;
-                d0 = fmaf(S[2 * i], kv.x, d0); d1 = fmaf(S[2 * i + 1], kv.y, d1);
+                S[2 * i] *= gc[i].x; S[2 * i + 1] *= gc[i].y;
+                d0 = fmaf(S[2 * i], kc[i].x, d0); d1 = fmaf(S[2 * i + 1], kc[i].y, d1);
             }
             float dot = d0 + d1;
 #pragma unroll
             for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = betas[t] * (vs[t][col] - dot);
+            const float u = bc * (vc - dot);
             d0 = d1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DL / 2; ++i) {
-                const float2 kv = kt[i], qv = qt[i];
-                S[2 * i] = fmaf(kv.x, u, S[2 * i]); S[2 * i + 1] = fmaf(kv.y, u, S[2 * i + 1]);
-                d0 = fmaf(S[2 * i], qv.x, d0); d1 = fmaf(S[2 * i + 1], qv.y, d1);
+                S[2 * i] = fmaf(kc[i].x, u, S[2 * i]); S[2 * i + 1] = fmaf(kc[i].y, u, S[2 * i + 1]);
+                d0 = fmaf(S[2 * i], qc[i].x, d0); d1 = fmaf(S[2 * i + 1], qc[i].y, d1);
             }
             float o = d0 + d1;
 #pragma unroll
@@ -814,15 +849,14 @@ delta_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gat
     }
 }
 
-template <typename T, int DL, int LANES>
+template <typename T, int DL, int LANES, int COLS>
 static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb, const T* a_in, int lda, const T* gate, int ldg,
                                    const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
                                    float q_scale, float* state, size_t state_stride, T* out, int ldo, float* o_raw,
-                                   const int* row_slot, const int* row_last, int n, int H, int G, int v_dim,
-                                   cudaStream_t stream) {
-    constexpr int COLS = LANES == 8 ? 64 : 32;
-    tis_launch(delta_rule_split_kernel<T, DL, LANES>, dim3(n, H, v_dim / COLS), dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
-               dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, H, G, v_dim);
+                                   const int* row_slot, const int* row_last, const int* seg_row0, int segments, int n,
+                                   int H, int G, int v_dim, cudaStream_t stream) {
+    tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS>, dim3(H, v_dim / COLS, seg_row0 != nullptr ? segments : n), dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
+               dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK) return st;
     tis_launch(delta_out_norm_kernel<T>, dim3((n * H + 3) / 4), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps,
@@ -844,7 +878,7 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
     }
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(delta_rule_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    tis_launch(delta_rule_kernel<T, DIM>, dim3(n, H), dim3(threads), smem, stream, qkv, ld, b_in, ldb, a_in, lda, gate, ldg,
+    tis_launch(delta_rule_kernel<T, DIM>, dim3(H, n), dim3(threads), smem, stream, qkv, ld, b_in, ldb, a_in, lda, gate, ldg,
                A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, out, ldo, row_slot, row_last, H, G,
                k_dim, v_dim);
     return tis_check_launch("delta_rule");
@@ -861,26 +895,36 @@ TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in,
                            const void* gate, int ldg, const float* A_log, const float* dt_bias, const float* norm_w,
                            float eps, float unit_eps, float q_scale, float* state, size_t state_stride, void* out,
                            int ldo, float* o_raw, const int* row_slot, const int* row_last, int n, int H, int G,
-                           int k_dim, int v_dim, cudaStream_t stream) {
+                           int k_dim, int v_dim, int narrow, const int* seg_row0, int segments, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
+    if (n > 65535) {
+        tis_set_error("delta_rule: %d rows in one step (at most 65535)", n);
+        return TIS_BAD_SIZE;
+    }
     if (o_raw != nullptr && H > 0 && G > 0 && H % G == 0 && tis_delta_rule_splits(k_dim, v_dim)) {
-#define TIS_DELTA_SPLIT(K, DL, LANES)                                                                                 \
+#define TIS_DELTA_SPLIT(K, DL, LANES, COLS)                                                                           \
     if (k_dim == K)                                                                                                    \
-        TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule_split<T, DL, LANES>((const T*)qkv, ld, (const T*)b_in,   \
-            ldb, (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state,      \
-            state_stride, (T*)out, ldo, o_raw, row_slot, row_last, n, H, G, v_dim, stream));
-        if (v_dim % 64 == 0) {                          // eight lanes a column, 64 columns a CTA
-            TIS_DELTA_SPLIT(32, 4, 8)
-            TIS_DELTA_SPLIT(64, 8, 8)
-            TIS_DELTA_SPLIT(96, 12, 8)
-            TIS_DELTA_SPLIT(128, 16, 8)
+        TIS_DISPATCH_DTYPE(dtype, T, return (launch_delta_rule_split<T, DL, LANES, COLS>((const T*)qkv, ld,            \
+            (const T*)b_in, ldb, (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps,      \
+            q_scale, state, state_stride, (T*)out, ldo, o_raw, row_slot, row_last, seg_row0, segments, n, H, G, v_dim, stream)));
+        if (v_dim % 64 == 0 && !narrow) {               // eight lanes a column, 64 columns a CTA
+            TIS_DELTA_SPLIT(32, 4, 8, 64)
+            TIS_DELTA_SPLIT(64, 8, 8, 64)
+            TIS_DELTA_SPLIT(96, 12, 8, 64)
+            TIS_DELTA_SPLIT(128, 16, 8, 64)
         }
-        TIS_DELTA_SPLIT(16, 4, 4)
-        TIS_DELTA_SPLIT(32, 8, 4)
-        TIS_DELTA_SPLIT(48, 12, 4)
-        TIS_DELTA_SPLIT(64, 16, 4)
-        TIS_DELTA_SPLIT(96, 24, 4)
-        TIS_DELTA_SPLIT(128, 32, 4)
+        if (v_dim % 16 == 0 && narrow) {                // eight lanes a column, 16 columns a CTA
+            TIS_DELTA_SPLIT(32, 4, 8, 16)
+            TIS_DELTA_SPLIT(64, 8, 8, 16)
+            TIS_DELTA_SPLIT(96, 12, 8, 16)
+            TIS_DELTA_SPLIT(128, 16, 8, 16)
+        }
+        TIS_DELTA_SPLIT(16, 4, 4, 32)
+        TIS_DELTA_SPLIT(32, 8, 4, 32)
+        TIS_DELTA_SPLIT(48, 12, 4, 32)
+        TIS_DELTA_SPLIT(64, 16, 4, 32)
+        TIS_DELTA_SPLIT(96, 24, 4, 32)
+        TIS_DELTA_SPLIT(128, 32, 4, 32)
 #undef TIS_DELTA_SPLIT
     }
     if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > 256) {

@@ -286,11 +286,11 @@ def seqmix(args, hbm_gbs=None, tflops=None):
     st = torch.zeros(max(B, 1), H * hd * hd, device=dev)
     od = torch.empty(n, nv, **bf)
     t_new = _graph_time(lambda i: ops.delta_rule(rows[i % 2], beta, a, gt, a_log, dtb, nw, 1e-6, 1e-6, hd ** -0.5, st, od, slot, last,
-                                                 H, G, hd, hd), 4)
+                                                 H, G, hd, hd, requests=1, segments=(torch.zeros(1, **i32), 1)), 4)
     put(f"delta rule, {n} rows of one request", t_new, 6.0 * n * H * hd * hd, "TFLOP/s")
     slot_b = torch.arange(B, **i32)
     t_new = _graph_time(lambda i: ops.delta_rule(rows[i % 2][:B], beta[:B], a[:B], gt[:B], a_log, dtb, nw, 1e-6, 1e-6, hd ** -0.5, st,
-                                                 od[:B], slot_b, slot_b, H, G, hd, hd), 12)
+                                                 od[:B], slot_b, slot_b, H, G, hd, hd, requests=B, segments=(slot_b, B)), 12)
     put(f"delta rule, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s")
     return out
 

@@ -916,18 +916,27 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     return out
 
 
+#: CTAs of 64 columns from which the delta rule keeps them (fewer: 16 columns a CTA, four times as many CTAs)
+DELTA_WIDE_MIN_CTAS = 2 * 148
+
+
 def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, gate: Optional[torch.Tensor],
                a_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float, unit_eps: float,
                q_scale: float, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor,
-               num_heads: int, qk_heads: int, k_dim: int, v_dim: int) -> torch.Tensor:
+               num_heads: int, qk_heads: int, k_dim: int, v_dim: int, requests: Optional[int] = None,
+               segments=None) -> torch.Tensor:
     """The delta rule with a decay per head and key channel over the rows of every request, from and into the
     requests' states ``state`` (slots, H, k_dim, v_dim) float32 (a view with a free slot stride).  A row of ``qkv``:
     queries and keys of ``qk_heads`` heads, values of ``num_heads`` heads.  Per head: q and k to unit length
     (``unit_eps`` inside the root; q times ``q_scale``), beta = sigmoid(``beta``), decay = exp(-exp(a_log) *
     softplus(``decay_in`` + dt_bias)) per key channel; S <- decay S; u = beta (v - S^T k); S <- S + k u^T;
-    o = S^T q; out = o / rms(o) * norm_weight * sigmoid(gate)."""
+    o = S^T q; out = o / rms(o) * norm_weight * sigmoid(gate).  ``requests``: how many requests the step holds, if
+    the caller knows (few requests: a head's columns are shared out over more CTAs).  ``segments``: (first rows of
+    the step's requests as an int32 device tensor, their number), from ``kernels.segment_plan``: the kernel then
+    launches CTAs for the requests only, not for every row."""
     lib = library()
     n = qkv.shape[0]
+    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
     # widths that the kernel with a head's columns split over CTAs takes: the outputs pass through 32-bit scratch
     # and a second launch normalises them
     raw = None
@@ -939,7 +948,8 @@ def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, ga
                               _p(gate), gate.stride(0) if gate is not None else 0, _p(a_log), _p(dt_bias), _p(norm_weight),
                               _f(eps), _f(unit_eps), _f(q_scale), _p(state), ctypes.c_size_t(state.stride(0)), _p(out),
                               out.stride(0), _p(raw), _p(row_slot), _p(row_last), n, num_heads, qk_heads, k_dim, v_dim,
-                              _stream()), lib)
+                              int(narrow), _p(segments[0] if segments is not None else None),
+                              int(segments[1]) if segments is not None else 0, _stream()), lib)
     return out
 
 

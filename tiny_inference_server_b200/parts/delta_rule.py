@@ -5,7 +5,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import ops, segment_plan
 from ..registry import register_part
 from .base import BuildContext, LayerBinding, Mixer, StateSpec, WeightSpec
 from .short_conv import CausalConv
@@ -63,6 +63,10 @@ class ChannelDeltaRule(Mixer):
     def children(self):
         return (self.conv,)
 
+    def step_planners(self):
+        # the first row of every request of the step: the recurrence launches a CTA per request
+        return (segment_plan.planner(),)
+
     def state_spec(self) -> StateSpec:
         return StateSpec((self.state_matrix + self.conv.state_floats,), torch.float32)
 
@@ -111,7 +115,8 @@ class ChannelDeltaRule(Mixer):
         ops.delta_rule(qkv, proj[:, self.beta_at:self.beta_at + self.num_heads], low[:, :self.na],
                        low[:, self.gate_at:self.gate_at + self.nv], self.a_log, self.dt_bias, self.norm_w, self.eps,
                        self.UNIT_EPS, self.k_dim ** -0.5, binding.state, out, step.row_slot, step.row_last,
-                       self.num_heads, self.qk_heads, self.k_dim, self.v_dim)
+                       self.num_heads, self.qk_heads, self.k_dim, self.v_dim, requests=len(step.segments),
+                       segments=step.plan(segment_plan.planner()))
         return ops.gemm(out, self.w_o)
 
 
