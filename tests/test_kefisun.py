@@ -64,8 +64,16 @@ K3 = dict(architecture="Kefisun", vocab=90, width=48, canon={"taps": 5}, embeddi
               {"type": "channel_delta", "mixer": _delta(3, 1, 12, 20, 4, (8, 24)), "mlp": _ff(40, 1.0)},
               {"type": "attention", "mixer": _attn(6, 3, 8, 8, 33, 3), "mlp": None},
           ])
-CONFIGS = {"K1": (K1, 16), "K2": (K2, 8), "K3": (K3, 12)}
-LENGTHS = {"K1": [1, 2, 3, 30, 75, 41, 9, 60], "K2": [1, 5, 40, 33, 17, 64], "K3": [2, 4, 50, 90, 23, 37]}
+# sizes that fit no vector, tile or alignment: every kernel's plain path, products with odd leading dimensions
+K4 = dict(architecture="Kefisun", vocab=53, width=40, canon={"taps": 7}, embedding={"scale": 2.0}, logit_scale=1.5,
+          norm={"eps": 1e-6}, layers=[
+              {"type": "channel_delta", "mixer": _delta(2, 1, 6, 10, 6, (3, 5)), "mlp": _ff(27, 1.0)},
+              {"type": "attention", "mixer": _attn(3, 1, 10, 6, 11, 6), "mlp": _ff(27, 1.0)},
+              {"type": "attention", "mixer": _attn(3, 1, 10, 6, 11, 6), "mlp": None},
+          ])
+CONFIGS = {"K1": (K1, 16), "K2": (K2, 8), "K3": (K3, 12), "K4": (K4, 16)}
+LENGTHS = {"K1": [1, 2, 3, 30, 75, 41, 9, 60], "K2": [1, 5, 40, 33, 17, 64], "K3": [2, 4, 50, 90, 23, 37],
+           "K4": [3, 1, 45, 20, 70]}
 
 
 def make_tensors(cfg, seed):
@@ -217,7 +225,7 @@ def test_config_errors_name_the_problem():
 # the engine's plumbing on the CPU
 # ------------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("name", ["K1", "K2", "K3"])
+@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_replay_cpu(name, mode, tmp_path, tmp_path_factory, ref_ops):
     raw, page, folder, seqs, ref, _, _ = _setup(name, tmp_path_factory)
@@ -524,7 +532,7 @@ def test_delta_rule_in_portions_and_far_memory(dtype, H, G, kd, vd):
 
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["K1", "K2", "K3"])
+@pytest.mark.parametrize("name", ["K1", "K2", "K3", "K4"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_replay_gpu(name, mode, dtype, tmp_path, tmp_path_factory):
     raw, page, folder, seqs, ref, _, _ = _setup(name, tmp_path_factory)
