@@ -31,12 +31,19 @@ class Block(Part):
         norm can then be folded into this block's last product and that block's first one."""
         mixer, ffn = self.mixer, self.ffn
         if self.input_filter is not None or ffn is None:
+            # the mixer reads the filter's output, whole rows; the norm before the feed-forward can still be folded
+            # into the mixer's last product and the feed-forward's first one
             a = stream.normed(self.norm_mixer)
             if self.input_filter is not None:
                 a = self.input_filter.forward(a, step, binding.filter_state)
-            stream.add(mixer.forward(a, step, binding))
-            if ffn is not None:
-                stream.add(ffn.forward(stream.normed(self.norm_ffn), step))
+            if ffn is None:
+                stream.add(mixer.forward(a, step, binding))
+                return
+            if mixer.fuses_residual and ffn.accepts_scaled_rows:
+                stream.add(mixer.forward(a, step, binding, residual=stream.sink(self.norm_ffn, a.dtype)))
+            else:
+                stream.add(mixer.forward(a, step, binding))
+            stream.add(ffn.forward(stream.normed(self.norm_ffn, scaled=ffn.accepts_scaled_rows), step))
             return
         a = stream.normed(self.norm_mixer, scaled=mixer.accepts_scaled_rows)
         if mixer.fuses_residual and ffn.accepts_scaled_rows:

@@ -30,6 +30,7 @@ class ChannelDeltaRule(Mixer):
     convolution's last inputs."""
 
     graph_safe = True
+    fuses_residual = True
     UNIT_EPS = 1e-6
 
     def __init__(self, width: int, num_heads: int, qk_heads: int, k_dim: int, v_dim: int, conv_taps: int, eps: float,
@@ -105,7 +106,7 @@ class ChannelDeltaRule(Mixer):
         self.dt_bias = tensors[p + "dt_bias"].to(**f32).contiguous()
         self.norm_w = tensors[p + "norm"].to(**f32).contiguous()
 
-    def forward(self, x, step, binding: LayerBinding):
+    def forward(self, x, step, binding: LayerBinding, residual=None):
         n = x.shape[0]
         proj = ops.gemm(x, self.w_in)
         nqkv = 2 * self.nq + self.nv
@@ -117,7 +118,7 @@ class ChannelDeltaRule(Mixer):
                        self.UNIT_EPS, self.k_dim ** -0.5, binding.state, out, step.row_slot, step.row_last,
                        self.num_heads, self.qk_heads, self.k_dim, self.v_dim, requests=len(step.segments),
                        segments=step.plan(segment_plan.planner()))
-        return ops.gemm(out, self.w_o)
+        return ops.gemm(out, self.w_o, sink=residual)
 
 
 register_part("mixer", "channel_delta_rule", ChannelDeltaRule)

@@ -64,6 +64,8 @@ class ClampedGLU(FeedForward):
     the bias of the down projection is one more row of its matrix, met by a column of ones that the gating
     kernel writes, so that the product adds it."""
 
+    accepts_scaled_rows = True
+
     def __init__(self, width: int, hidden: int, limit: float, alpha: float = 1.702, shift: float = 1.0,
                  prefix: str = ""):
         super().__init__(prefix)
@@ -97,7 +99,7 @@ class ClampedGLU(FeedForward):
 
     def forward(self, x, step=None):
         gu = ops.gemm(x, self.w_gate_up)
-        y = torch.empty((x.shape[0], self.padded), dtype=x.dtype, device=x.device)
+        y = torch.empty((gu.shape[0], self.padded), dtype=gu.dtype, device=gu.device)
         ops.glu_clamped(gu, self.b_gate, self.b_up, self.limit, self.alpha, self.shift, y, self.hidden)
         return ops.gemm(y, self.w_down)
 

@@ -43,6 +43,7 @@ class BiasedWindowAttention(Mixer):
     ``q.norm, k.norm``, ``r1, r2``, ``vmix``, ``g``."""
 
     graph_safe = True
+    fuses_residual = True
 
     def __init__(self, width: int, num_heads: int, kv_heads: int, k_dim: int, v_dim: int, scale: float,
                  window: Optional[int], eps: float, conv_taps: Optional[int] = None, qk_norm: bool = True,
@@ -122,7 +123,7 @@ class BiasedWindowAttention(Mixer):
         if self.value_share is not None:
             self.mix = tensors[p + "vmix"].to(**f32).reshape(1).contiguous()
 
-    def forward(self, x, step, binding: LayerBinding):
+    def forward(self, x, step, binding: LayerBinding, residual=None):
         n = x.shape[0]
         g = binding.kv_group
         table, page_size = step.block_tables[g], step.page_sizes[g]
@@ -142,7 +143,7 @@ class BiasedWindowAttention(Mixer):
         ops.window_attention(qkv[:, :self.nq], gate, out, binding.k_pages, binding.v_pages, table, step.positions,
                              step.row_slot, self.num_heads, page_size, self.window, self.scale, self.r1, self.r2,
                              step.fault, step)
-        return ops.gemm(out, self.w_o)
+        return ops.gemm(out, self.w_o, sink=residual)
 
 
 register_part("mixer", "biased_window_attention", BiasedWindowAttention)
