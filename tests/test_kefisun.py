@@ -588,3 +588,38 @@ def test_generate_through_the_scheduler(tmp_path, tmp_path_factory):
     eng = Engine.from_folder(folder, EngineConfig(dtype="bfloat16", page_size=page, num_pages=40, max_batch=4))
     out = eng.generate(prompts, sp)
     assert [len(o) for o in out] == [10] * 4 and eng.runner.cache.drained()
+
+
+@gpu
+def test_command_line_generation_with_chunking_and_preemption(tmp_path, tmp_path_factory):
+    """Greedy tokens through ``python -m tiny_inference_server_b200.cli`` equal the plain implementation's: whole
+    prompts; a token budget of five (portions beside decoding requests); and so few pages that requests are preempted
+    and fed again from their first token (their recurrent state and convolution histories start from zero again)."""
+    from test_cli import _cli, _ids
+    raw, page, folder, seqs, _, c, W = _setup("K3", tmp_path_factory)
+    new = 8
+    prompts = [seqs["r0"], seqs["r4"], seqs["r1"]]
+    want = [plain_greedy(c, W, p, new) for p in prompts]
+    args = ["--model", folder, "--greedy", "--ignore-eos", "--dtype", "float32", "--max-new-tokens", new,
+            "--tokens-per-block", page, "--json"]
+    for p in prompts:
+        args += ["--prompt-ids", _ids(p)]
+    r = _cli(*args)
+    assert r.returncode == 0, r.stderr
+    assert json.loads(r.stdout.strip().splitlines()[-1])["outputs"] == want
+    r = _cli(*args, "--max-tokens-per-step", 5, "--max-batch", 2)
+    assert r.returncode == 0, r.stderr
+    assert json.loads(r.stdout.strip().splitlines()[-1])["outputs"] == want
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, raw["vocab"], (page - 1,), generator=g).tolist() for _ in range(4)]
+    want = [plain_greedy(c, W, p, new) for p in prompts]
+    args = ["--model", folder, "--greedy", "--ignore-eos", "--dtype", "float32", "--max-new-tokens", new,
+            "--tokens-per-block", page, "--json", "--num-pages", 5, "--plan", "cur", "--max-batch", 4,
+            "--max-tokens-per-step", 16]
+    for p in prompts:
+        args += ["--prompt-ids", _ids(p)]
+    r = _cli(*args)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["outputs"] == want
+    assert out["stats"]["preempts"] > 0 and out["stats"]["replays"] > 0
