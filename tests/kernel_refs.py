@@ -161,7 +161,7 @@ def norm_mix_store(qkv, nq, nk, nv, q_weight, k_weight, eps, v_other, mix, k_pag
 
 
 def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row_slot, num_heads, page_size, window,
-                     scale, bias_slope, bias_rate, fault, step=None):
+                     scale, bias_slope, bias_rate, fault, step=None, sink=None):
     kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
     g = num_heads // kv_heads
     for r in range(q.shape[0]):
@@ -178,7 +178,10 @@ def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row
         s = torch.einsum("hd,khd->hk", qq, k) * scale
         if bias_slope is not None:
             s = s - bias_slope[:, None] * torch.log(1.0 + bias_rate[:, None] * (pos - idx).to(torch.float32)[None, :])
-        o = torch.einsum("hk,khd->hd", torch.softmax(s, dim=-1), v).reshape(-1)
+        if sink is not None:               # one more term in the denominator, without a value
+            s = torch.cat([s, sink.to(torch.float32)[:, None]], dim=-1)
+        w = torch.softmax(s, dim=-1)[:, :idx.shape[0]]
+        o = torch.einsum("hk,khd->hd", w, v).reshape(-1)
         if gate is not None:
             o = o * torch.sigmoid(gate[r].to(torch.float32))
         out[r] = o.to(out.dtype)
@@ -186,7 +189,8 @@ def window_attention(q, gate, out, k_pages, v_pages, block_table, positions, row
 
 
 def delta_rule(qkv, beta, decay_in, gate, a_log, dt_bias, norm_weight, eps, unit_eps, q_scale, state, out, row_slot,
-               row_last, num_heads, qk_heads, k_dim, v_dim, requests=None, segments=None):
+               row_last, num_heads, qk_heads, k_dim, v_dim, requests=None, segments=None, decay_per_head=False,
+               gate_act="sigmoid"):
     H, G = num_heads, qk_heads
     nq = G * k_dim
     rate = torch.exp(a_log.to(torch.float32))[:, None]
@@ -200,17 +204,111 @@ def delta_rule(qkv, beta, decay_in, gate, a_log, dt_bias, norm_weight, eps, unit
             q = (q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * q_scale).repeat_interleave(H // G, dim=0)
             k = (k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(H // G, dim=0)
             b = torch.sigmoid(beta[r].to(torch.float32))[:, None]
-            a = decay_in[r].to(torch.float32).view(H, k_dim) + dt_bias.view(H, k_dim)
+            if decay_per_head:
+                a = (decay_in[r].to(torch.float32) + dt_bias)[:, None]
+            else:
+                a = decay_in[r].to(torch.float32).view(H, k_dim) + dt_bias.view(H, k_dim)
             S = torch.exp(-rate * torch.nn.functional.softplus(a))[:, :, None] * S
             u = b * (v - torch.einsum("hdv,hd->hv", S, k))
             S = S + k[:, :, None] * u[:, None, :]
             o = torch.einsum("hdv,hd->hv", S, q)
             o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_weight
             if gate is not None:
-                o = o * torch.sigmoid(gate[r].to(torch.float32).view(H, v_dim))
+                gv = gate[r].to(torch.float32).view(H, v_dim)
+                o = o * (torch.sigmoid(gv) if gate_act == "sigmoid" else gv * torch.sigmoid(gv))
             out[r] = o.reshape(-1).to(out.dtype)
         state[slot, :H * k_dim * v_dim] = S.reshape(-1)
     return out
+
+
+def linear_attention(qkv, gate, decay, norm_weight, eps, state, out, row_slot, row_last, num_heads, k_dim, v_dim,
+                     requests=None, segments=None):
+    H = num_heads
+    nq = H * k_dim
+    act = torch.nn.functional.silu
+    for r0, rows, slot in _segments(row_slot):
+        S = state[slot, :H * k_dim * v_dim].reshape(H, k_dim, v_dim).to(torch.float32).clone()
+        for r in range(r0, r0 + rows):
+            row = qkv[r].to(torch.float32)
+            q, k = act(row[:nq]).view(H, k_dim), act(row[nq:2 * nq]).view(H, k_dim)
+            v = act(row[2 * nq:2 * nq + H * v_dim]).view(H, v_dim)
+            S = decay.to(torch.float32)[:, None, None] * S + k[:, :, None] * v[:, None, :]
+            o = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+            o = o / torch.sqrt(o.pow(2).mean() + eps) * norm_weight
+            if gate is not None:
+                o = o * torch.sigmoid(gate[r].to(torch.float32))
+            out[r] = o.to(out.dtype)
+        state[slot, :H * k_dim * v_dim] = S.reshape(-1)
+    return out
+
+
+def latent_prepare(proj, dkv_at, num_heads, flat_dim, rot_dim, rank, c_weight, eps, cos, sin, q_out, k_pages, block_table,
+                   positions, row_slot, page_size, fault):
+    half = rot_dim // 2
+    qd, row_w = flat_dim + rot_dim, rank + rot_dim
+
+    def turn(x, c, s):
+        a, b = x[..., :half], x[..., half:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    for r in range(proj.shape[0]):
+        slot = int(row_slot[r])
+        if slot < 0:
+            continue
+        pos = int(positions[r])
+        row = proj[r].to(torch.float32)
+        c, s = cos[pos], sin[pos]
+        q_rot = row[:num_heads * qd].view(num_heads, qd)[:, flat_dim:]
+        q_out[r].view(num_heads, row_w)[:, rank:] = turn(q_rot, c, s).to(q_out.dtype)
+        low = row[dkv_at:dkv_at + row_w]
+        latent = low[:rank] / torch.sqrt(low[:rank].pow(2).mean() + eps) * c_weight
+        page = int(block_table[slot, pos // page_size])
+        if page < 0 or page >= k_pages.shape[0]:
+            fault[0] = 6
+            continue
+        k_pages[page, 0, pos % page_size, :] = torch.cat([latent, turn(low[rank:], c, s)]).to(k_pages.dtype)
+
+
+def gemm_heads(a, w, out):
+    out.copy_(torch.einsum("nhk,hkj->nhj", a.to(torch.float32), w.to(torch.float32)).to(out.dtype))
+    return out
+
+
+def moe_route(x, w_router, correction, w_shared_gate, groups, keep, top, weight_eps=1e-20):
+    xf = x.to(torch.float32)
+    s = torch.sigmoid(xf @ w_router.t())
+    n, experts = s.shape
+    pick = s + correction if correction is not None else s.clone()
+    if groups:
+        per = pick.view(n, groups, experts // groups)
+        strength = per.topk(min(2, experts // groups), dim=-1).values.sum(-1)
+        best = strength.topk(keep, dim=-1).indices
+        ok = torch.zeros((n, groups), dtype=torch.bool).scatter_(1, best, True)
+        pick = per.masked_fill(~ok[:, :, None], float("-inf")).reshape(n, experts)
+    chosen = pick.topk(top, dim=-1).indices
+    w = s.gather(1, chosen)
+    w = w / (w.sum(-1, keepdim=True) + weight_eps)
+    shared = torch.sigmoid(xf @ w_shared_gate) if w_shared_gate is not None else None
+    return chosen.to(torch.int32), w, shared
+
+
+def moe_gate_up(x, chosen, w_gate_up):
+    n, top = chosen.shape
+    xf = x.to(torch.float32)
+    w = w_gate_up.to(torch.float32)[chosen.long()]                      # (n, top, 2, F, d)
+    g = torch.einsum("ntfd,nd->ntf", w[:, :, 0], xf)
+    u = torch.einsum("ntfd,nd->ntf", w[:, :, 1], xf)
+    return (g * torch.sigmoid(g) * u).reshape(n * top, -1).to(x.dtype)
+
+
+def moe_down(hidden, chosen, weights, w_down, shared, shared_gate):
+    n, top = chosen.shape
+    h = hidden.to(torch.float32).view(n, top, -1)
+    y = torch.einsum("ntdf,ntf->ntd", w_down.to(torch.float32)[chosen.long()], h)
+    out = (y * weights[:, :, None]).sum(1)
+    if shared is not None:
+        out = out + shared_gate[:, None] * shared.to(torch.float32)
+    return out.to(hidden.dtype)
 
 
 def residual_add(residual, delta):
@@ -455,7 +553,8 @@ def bitmap_set(bitmap_row, tokens):
 
 _NAMES = ["rotary_fusable", "gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
           "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set", "glu_clamped", "scale_f32", "causal_conv",
-          "norm_mix_store", "window_attention", "delta_rule"]
+          "norm_mix_store", "window_attention", "delta_rule", "linear_attention", "latent_prepare", "gemm_heads", "moe_route",
+          "moe_gate_up", "moe_down"]
 
 
 def install(monkeypatch) -> None:

@@ -341,3 +341,143 @@ class KefisunConfig:
         if self.eos_token_id is not None:
             d["eos_token_id"] = self.eos_token_id
         return d
+
+
+def _positive_int(v) -> bool:
+    return isinstance(v, int) and not isinstance(v, bool) and v > 0
+
+
+@dataclass
+class MizidraConfig:
+    """Configuration of the Mizidra decoder: a normed embedding, pre-norm layers whose mixer is one of three kinds
+    and whose feed-forward, where a layer has one, is a routed mixture of small gated units; an output matrix of
+    its own.
+
+    ``config.json`` is nested: ``vocab``, ``width``, ``norm.eps`` and ``layers``, a list with, per layer, ``type``,
+    ``mixer`` (the sizes and constants of that kind of mixer) and ``mlp`` (null: none).  The kinds:
+
+    * ``delta`` — ``heads, kv_heads, dim, vdim, conv``: the delta rule with one decay per head;
+    * ``latent_attention`` — ``heads, dim, rot_dim, vdim, kv_rank, scale, rot`` (``base, dims`` and, optionally,
+      ``scaling`` = ``factor, original, fast, slow``): attention whose keys and values are expanded from a
+      compressed vector per token, with a rotated slice and a keyless term in the softmax;
+    * ``lightning`` — ``heads, dim, vdim, decay`` (one constant per head): linear attention with a fixed decay.
+
+    ``mlp``: ``kind`` ``moe``, ``expert.ff``, ``router`` = ``experts, top`` and optionally ``groups`` = ``count,
+    keep``, and optionally ``shared.ff``.  The design has no context limit of its own: ``max_context`` (optional)
+    bounds what the engine lays out (block tables, rotation tables)."""
+
+    architecture: ClassVar[str] = "Mizidra"
+    MIXERS: ClassVar[tuple] = ("delta", "latent_attention", "lightning")
+
+    vocab_size: int
+    hidden_size: int
+    layers: list
+    rms_norm_eps: float = 1e-6
+    max_context: int = 1 << 16
+    eos_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        errs = []
+        for name in ("vocab_size", "hidden_size"):
+            if not _positive_int(getattr(self, name)):
+                errs.append(f"{name} must be a positive integer, got {getattr(self, name)!r}")
+        if not isinstance(self.layers, list) or not self.layers:
+            errs.append("layers must be a non-empty list")
+            raise ConfigError("; ".join(errs))
+        if not (self.rms_norm_eps >= 0):
+            errs.append(f"norm.eps must be >= 0, got {self.rms_norm_eps}")
+        if not _positive_int(self.max_context):
+            errs.append(f"max_context must be positive, got {self.max_context}")
+        for i, layer in enumerate(self.layers):
+            kind = layer.get("type") if isinstance(layer, dict) else None
+            if kind not in self.MIXERS:
+                errs.append(f"layers[{i}].type must be one of {self.MIXERS}, got {kind!r}")
+                continue
+            m = layer.get("mixer")
+            if not isinstance(m, dict):
+                errs.append(f"layers[{i}].mixer is missing")
+                continue
+            need = {"delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
+                    "latent_attention": ("heads", "dim", "rot_dim", "vdim", "kv_rank"),
+                    "lightning": ("heads", "dim", "vdim")}[kind]
+            bad = [k for k in need if not _positive_int(m.get(k))]
+            if bad:
+                errs.append(f"layers[{i}].mixer: {', '.join(bad)} must be positive integers")
+                continue
+            if kind == "delta":
+                if m["heads"] % m["kv_heads"]:
+                    errs.append(f"layers[{i}].mixer: {m['heads']} heads are not a multiple of {m['kv_heads']} kv heads")
+                if m["conv"] > 16:
+                    errs.append(f"layers[{i}].mixer.conv must be 1..16, got {m['conv']}")
+            elif kind == "latent_attention":
+                if not isinstance(m.get("scale"), (int, float)):
+                    errs.append(f"layers[{i}].mixer.scale is missing")
+                rot = m.get("rot")
+                if not isinstance(rot, dict) or not isinstance(rot.get("base"), (int, float)) or rot["base"] <= 0:
+                    errs.append(f"layers[{i}].mixer.rot.base is missing")
+                elif rot.get("dims", m["rot_dim"]) != m["rot_dim"] or m["rot_dim"] % 2:
+                    errs.append(f"layers[{i}].mixer: rot.dims must equal rot_dim ({m['rot_dim']}) and be even")
+                elif rot.get("scaling"):
+                    sc = rot["scaling"]
+                    miss = [k for k in ("factor", "original", "fast", "slow") if not isinstance(sc.get(k), (int, float))]
+                    if miss:
+                        errs.append(f"layers[{i}].mixer.rot.scaling lacks {', '.join(miss)}")
+            else:
+                d = m.get("decay")
+                if not isinstance(d, list) or len(d) != m["heads"] or not all(isinstance(v, (int, float)) for v in d):
+                    errs.append(f"layers[{i}].mixer.decay must list one number per head")
+            f = layer.get("mlp")
+            if f is None:
+                continue
+            if not isinstance(f, dict) or f.get("kind") != "moe":
+                errs.append(f"layers[{i}].mlp.kind must be 'moe', got {f.get('kind') if isinstance(f, dict) else f!r}")
+                continue
+            r = f.get("router")
+            if not isinstance(f.get("expert"), dict) or not _positive_int(f["expert"].get("ff")):
+                errs.append(f"layers[{i}].mlp.expert.ff must be a positive integer")
+            if not isinstance(r, dict) or not _positive_int(r.get("experts")) or not _positive_int(r.get("top")):
+                errs.append(f"layers[{i}].mlp.router needs experts and top")
+                continue
+            g = r.get("groups")
+            allowed = r["experts"]
+            if g:
+                if not _positive_int(g.get("count")) or not _positive_int(g.get("keep")) or r["experts"] % g["count"] \
+                        or g["keep"] > g["count"]:
+                    errs.append(f"layers[{i}].mlp.router.groups: count must divide the experts and keep <= count")
+                    continue
+                allowed = r["experts"] // g["count"] * g["keep"]
+            if r["top"] > allowed:
+                errs.append(f"layers[{i}].mlp.router.top {r['top']} exceeds the {allowed} experts that can be chosen")
+            s = f.get("shared")
+            if s and not _positive_int(s.get("ff")):
+                errs.append(f"layers[{i}].mlp.shared.ff must be a positive integer")
+        if self.torch_dtype not in ("bfloat16", "float32"):
+            errs.append(f"torch_dtype must be bfloat16 or float32, got {self.torch_dtype!r}")
+        if errs:
+            raise ConfigError("; ".join(errs))
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "MizidraConfig":
+        missing = [k for k in ("vocab", "width", "layers") if k not in raw]
+        if missing:
+            raise ConfigError(f"config for architecture {cls.architecture!r}: missing keys: " + ", ".join(missing))
+        d = dict(vocab_size=raw["vocab"], hidden_size=raw["width"], layers=copy.deepcopy(raw["layers"]))
+        if isinstance(raw.get("norm"), dict) and "eps" in raw["norm"]:
+            d["rms_norm_eps"] = float(raw["norm"]["eps"])
+        for k in ("max_context", "eos_token_id", "torch_dtype"):
+            if k in raw:
+                d[k] = raw[k]
+        return cls(**d)
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+             "norm": {"eps": self.rms_norm_eps}, "layers": copy.deepcopy(self.layers), "max_context": self.max_context,
+             "torch_dtype": self.torch_dtype}
+        if self.eos_token_id is not None:
+            d["eos_token_id"] = self.eos_token_id
+        return d

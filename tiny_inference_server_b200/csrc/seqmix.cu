@@ -406,7 +406,8 @@ window_attention_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                         const int* __restrict__ block_table, int bt_stride, int num_pages,
                         const int* __restrict__ positions, const int* __restrict__ row_slot, int H, int G, int k_dim,
                         int v_dim, int page_size, int window, float scale, const float* __restrict__ r1,
-                        const float* __restrict__ r2, int* __restrict__ fault) {
+                        const float* __restrict__ r2, const float* __restrict__ sink, int v_row,
+                        int* __restrict__ fault) {
     extern __shared__ float smem[];
     __shared__ float red[33];
     __shared__ int page_of[WA_THREADS];
@@ -433,7 +434,8 @@ window_attention_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
     float acc[WA_MAX_COLS];
 #pragma unroll
     for (int a = 0; a < WA_MAX_COLS; ++a) acc[a] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    // a sink is one more term of the denominator, exp(sink[head]), with no value: the running maximum starts there
+    float m = sink != nullptr ? sink[head] : -INFINITY, l = sink != nullptr ? 1.f : 0.f;
     __syncthreads();
     for (int base = lo; base < hi; base += WA_THREADS) {
         const int j = base + tid;
@@ -469,7 +471,7 @@ window_attention_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                 if (pg < 0) continue;
                 const float pt = ps[t];
                 const T* vr = v_pages + (size_t)pg * v_page_stride + (size_t)kvh * v_head_stride +
-                              (size_t)((base + t) % page_size) * v_dim;
+                              (size_t)((base + t) % page_size) * v_row;
 #pragma unroll
                 for (int a = 0; a < WA_MAX_COLS; ++a) {
                     const int c = col0 + a * WA_THREADS;
@@ -510,10 +512,10 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
                                  size_t v_page_stride, size_t v_head_stride, const int* block_table, int bt_stride,
                                  int num_pages, const int* positions, const int* row_slot, int n, int H, int G,
                                  int k_dim, int v_dim, int page_size, int window, float scale, const float* r1,
-                                 const float* r2, int* fault, cudaStream_t stream) {
+                                 const float* r2, const float* sink, int v_row, int* fault, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     if (H <= 0 || G <= 0 || H % G || k_dim <= 0 || v_dim <= 0 || v_dim > WA_THREADS * WA_MAX_COLS || page_size <= 0 ||
-        window < 0) {
+        window < 0 || v_row < v_dim) {
         tis_set_error("window_attention: %d query heads, %d kv heads, key width %d, value width %d (at most %d), "
                       "page size %d, window %d", H, G, k_dim, v_dim, WA_THREADS * WA_MAX_COLS, page_size, window);
         return TIS_BAD_SIZE;
@@ -524,7 +526,7 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
         tis_launch(window_attention_kernel<T>, dim3(n, H), dim3(WA_THREADS), smem, stream, (const T*)q, ldq,
                    (const T*)gate, ldg, (T*)out, ldo, (const T*)k_pages, k_page_stride, k_head_stride, (const T*)v_pages,
                    v_page_stride, v_head_stride, block_table, bt_stride, num_pages, positions, row_slot, H, G, k_dim,
-                   v_dim, page_size, window, scale, r1, r2, fault));
+                   v_dim, page_size, window, scale, r1, r2, sink, v_row, fault));
     return tis_check_launch("window_attention");
 }
 
@@ -545,6 +547,13 @@ TIS_API int tis_window_attention(int dtype, const void* q, int ldq, const void* 
 constexpr int DELTA_CHUNK = 16;
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+// what a gate does to the projection it is made from: 0 sigmoid, 1 silu
+__device__ __forceinline__ float gate_f(float x, int act) { const float s = 1.f / (1.f + expf(-x)); return act == 1 ? x * s : s; }
+// where the decay of a token comes from: a projection per head and key channel, a projection per head, or a constant
+// per head (`A_log` then holds the constants themselves and the recurrence is plain linear attention: q, k and v pass
+// silu instead of the unit norms, and the state takes k v^T without the correction towards v)
+enum { DECAY_PER_CHANNEL = 0, DECAY_PER_HEAD = 1, DECAY_CONSTANT = 2 };
 
 template <typename T, int DIM>
 __global__ void __launch_bounds__(256)
@@ -553,7 +562,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                   const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps, float unit_eps,
                   float q_scale, float* __restrict__ state, size_t state_stride, T* __restrict__ out, int ldo,
                   const int* __restrict__ row_slot, const int* __restrict__ row_last, int H, int G, int k_dim_rt,
-                  int v_dim) {
+                  int v_dim, int decay_mode, int gate_act, float* __restrict__ o_raw) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
     const int head = blockIdx.x, r0 = blockIdx.y;
@@ -571,7 +580,8 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
     float* os = vs + DELTA_CHUNK * v_dim;               // [CHUNK][v_dim]
     float* betas = os + DELTA_CHUNK * v_dim;            // [CHUNK]
     float* S_sh = betas + DELTA_CHUNK;                  // [k_dim][v_dim] when DIM == 0
-    const float decay_rate = expf(A_log[head]);
+    const bool plain = decay_mode == DECAY_CONSTANT;
+    const float decay_rate = plain ? A_log[head] : expf(A_log[head]);
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * k_dim * v_dim;
     constexpr int REG = DIM > 0 ? DIM : 1;
     float S[REG];
@@ -599,10 +609,22 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
             sq = warp_sum(sq);
             sk = warp_sum(sk);
             const float fq = q_scale / sqrtf(sq + unit_eps), fk = 1.f / sqrtf(sk + unit_eps);
+            if (plain) {
+                for (int i = lane; i < k_dim; i += 32) {
+                    qs[t * k_dim + i] = silu_f(to_f32(row[q_off + i]));
+                    ks[t * k_dim + i] = silu_f(to_f32(row[k_off + i]));
+                    gs[t * k_dim + i] = decay_rate;
+                }
+                for (int j = lane; j < v_dim; j += 32) vs[t * v_dim + j] = silu_f(to_f32(row[v_off + j]));
+                if (lane == 0) betas[t] = 1.f;
+                continue;
+            }
+            const size_t a_at = decay_mode == DECAY_PER_HEAD ? (size_t)head : (size_t)head * k_dim;
+            const int a_step = decay_mode == DECAY_PER_HEAD ? 0 : 1;
             for (int i = lane; i < k_dim; i += 32) {
                 qs[t * k_dim + i] = to_f32(row[q_off + i]) * fq;
                 ks[t * k_dim + i] = to_f32(row[k_off + i]) * fk;
-                const float a = to_f32(a_in[(size_t)(r0 + c0 + t) * lda + head * k_dim + i]) + dt_bias[head * k_dim + i];
+                const float a = to_f32(a_in[(size_t)(r0 + c0 + t) * lda + a_at + i * a_step]) + dt_bias[a_at + i * a_step];
                 gs[t * k_dim + i] = expf(-decay_rate * softplus_f(a));
             }
             for (int j = lane; j < v_dim; j += 32) vs[t * v_dim + j] = to_f32(row[v_off + j]);
@@ -624,7 +646,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                         S[i] *= gt[i];
                         dot = fmaf(S[i], kt[i], dot);
                     }
-                    const float u = betas[t] * (vs[t * v_dim + tid] - dot);
+                    const float u = plain ? vs[t * v_dim + tid] : betas[t] * (vs[t * v_dim + tid] - dot);
 #pragma unroll
                     for (int i = 0; i < REG; ++i) {
                         S[i] = fmaf(kt[i], u, S[i]);
@@ -636,7 +658,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
                         S_sh[i * v_dim + tid] = s;
                         dot = fmaf(s, kt[i], dot);
                     }
-                    const float u = betas[t] * (vs[t * v_dim + tid] - dot);
+                    const float u = plain ? vs[t * v_dim + tid] : betas[t] * (vs[t * v_dim + tid] - dot);
                     for (int i = 0; i < k_dim; ++i) {
                         const float s = fmaf(kt[i], u, S_sh[i * v_dim + tid]);
                         S_sh[i * v_dim + tid] = s;
@@ -647,6 +669,13 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
             }
         }
         __syncthreads();
+        if (o_raw != nullptr) {                         // the outputs leave as they are, for a norm over whole rows
+            for (int idx = tid; idx < cnt * v_dim; idx += nthr) {
+                const int t = idx / v_dim, j = idx - t * v_dim;
+                o_raw[(size_t)(r0 + c0 + t) * H * v_dim + (size_t)head * v_dim + j] = os[idx];
+            }
+            continue;
+        }
         for (int t = warp; t < cnt; t += nwarps) {
             float ss = 0.f;
             for (int j = lane; j < v_dim; j += 32) { const float o = os[t * v_dim + j]; ss += o * o; }
@@ -655,10 +684,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
             const size_t rr = (size_t)(r0 + c0 + t);
             for (int j = lane; j < v_dim; j += 32) {
                 float o = os[t * v_dim + j] * f * norm_w[j];
-                if (gate != nullptr) {
-                    const float gv = to_f32(gate[rr * ldg + head * v_dim + j]);
-                    o = o / (1.f + expf(-gv));
-                }
+                if (gate != nullptr) o *= gate_f(to_f32(gate[rr * ldg + head * v_dim + j]), gate_act);
                 out[rr * ldo + head * v_dim + j] = from_f32<T>(o);
             }
         }
@@ -688,7 +714,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
                         int lda, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
                         float q_scale, float* __restrict__ state, size_t state_stride, float* __restrict__ o_raw,
                         const int* __restrict__ row_slot, const int* __restrict__ row_last,
-                        const int* __restrict__ seg_row0, int H, int G, int v_dim) {
+                        const int* __restrict__ seg_row0, int H, int G, int v_dim, int decay_mode) {
     constexpr int KDIM = LANES * DL, QP = DL + 4, ROW = LANES * QP, NT = COLS * LANES;
     constexpr int PT = NT / DELTA_CHUNK;                // threads that prepare a token
     constexpr int CH = KDIM / PT, VPT = COLS / PT;      // key channels and value columns of each
@@ -710,7 +736,8 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int kvh = head / (H / G);
     const int tid = threadIdx.x;
     const int col = tid / LANES, part = tid % LANES;
-    const float decay_rate = expf(A_log[head]);
+    const bool plain = decay_mode == DECAY_CONSTANT;
+    const float decay_rate = plain ? A_log[head] : expf(A_log[head]);
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
     float S[DL];
     pdl_wait();
@@ -719,6 +746,8 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int q_off = kvh * KDIM, k_off = G * KDIM + kvh * KDIM, v_off = 2 * G * KDIM + head * v_dim + col0;
     const int nv = H * v_dim;
     const int pt = tid / PT, sub = tid % PT;
+    const size_t a_at = decay_mode == DECAY_PER_HEAD ? (size_t)head : (size_t)head * KDIM;
+    const int a_step = decay_mode == DECAY_PER_HEAD ? 0 : 1;
     float rq[CH], rk[CH], ra[CH], rv[VPT], rb = 0.f;
     auto fetch = [&](int c0) {
         const bool live = c0 + pt < rows;
@@ -728,15 +757,15 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
         for (int i = 0; i < CH; ++i) {
             rq[i] = live ? to_f32(row[q_off + sub * CH + i]) : 0.f;
             rk[i] = live ? to_f32(row[k_off + sub * CH + i]) : 0.f;
-            ra[i] = live ? to_f32(a_in[rr * lda + head * KDIM + sub * CH + i]) : 0.f;
+            ra[i] = (live && !plain) ? to_f32(a_in[rr * lda + a_at + (sub * CH + i) * a_step]) : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < VPT; ++i) rv[i] = live ? to_f32(row[v_off + sub * VPT + i]) : 0.f;
-        rb = (live && sub == 0) ? to_f32(b_in[rr * ldb + head]) : 0.f;
+        rb = (live && sub == 0 && !plain) ? to_f32(b_in[rr * ldb + head]) : 0.f;
     };
     float bias[CH];
 #pragma unroll
-    for (int i = 0; i < CH; ++i) bias[i] = dt_bias[head * KDIM + sub * CH + i];
+    for (int i = 0; i < CH; ++i) bias[i] = plain ? 0.f : dt_bias[a_at + (sub * CH + i) * a_step];
     fetch(0);
     for (int c0 = 0; c0 < rows; c0 += DELTA_CHUNK) {
         const int cnt = min(DELTA_CHUNK, rows - c0);
@@ -755,12 +784,12 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             for (int i = 0; i < CH; ++i) {
                 const int ch = sub * CH + i;
                 const int at = ch + (ch / DL) * 4;
-                qs[pt][at] = rq[i] * fq;
-                ks[pt][at] = rk[i] * fk;
-                gs[pt][at] = expf(-decay_rate * softplus_f(ra[i] + bias[i]));
+                qs[pt][at] = plain ? silu_f(rq[i]) : rq[i] * fq;
+                ks[pt][at] = plain ? silu_f(rk[i]) : rk[i] * fk;
+                gs[pt][at] = plain ? decay_rate : expf(-decay_rate * softplus_f(ra[i] + bias[i]));
             }
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) vs[pt][sub * VPT + i] = rv[i];
+            for (int i = 0; i < VPT; ++i) vs[pt][sub * VPT + i] = plain ? silu_f(rv[i]) : rv[i];
             if (sub == 0) betas[pt] = 1.f / (1.f + expf(-rb));
         }
         __syncthreads();
@@ -809,7 +838,7 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
             float dot = d0 + d1;
 #pragma unroll
             for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = bc * (vc - dot);
+            const float u = plain ? vc : bc * (vc - dot);
             d0 = d1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DL / 2; ++i) {
@@ -830,7 +859,8 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
 template <typename T>
 __global__ void __launch_bounds__(128)
 delta_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gate, int ldg, const float* __restrict__ norm_w,
-                      float eps, T* __restrict__ out, int ldo, const int* __restrict__ row_slot, int n, int H, int v_dim) {
+                      float eps, T* __restrict__ out, int ldo, const int* __restrict__ row_slot, int n, int H, int v_dim,
+                      int gate_act) {
     pdl_launch_dependents();
     const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (idx >= n * H) return;
@@ -844,8 +874,31 @@ delta_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gat
     const float f = rsqrtf(ss / (float)v_dim + eps);
     for (int j = lane; j < v_dim; j += 32) {
         float x = o[j] * f * norm_w[j];
-        if (gate != nullptr) x = x / (1.f + expf(-to_f32(gate[(size_t)r * ldg + head * v_dim + j])));
+        if (gate != nullptr) x *= gate_f(to_f32(gate[(size_t)r * ldg + head * v_dim + j]), gate_act);
         out[(size_t)r * ldo + head * v_dim + j] = from_f32<T>(x);
+    }
+}
+
+// out[r, :] = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate) over the whole row (`width` elements, all heads
+// together): a CTA a row.
+template <typename T>
+__global__ void __launch_bounds__(128)
+row_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gate, int ldg, const float* __restrict__ norm_w,
+                    float eps, T* __restrict__ out, int ldo, const int* __restrict__ row_slot, int width) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    if (row_slot[r] < 0) return;
+    pdl_wait();
+    const float* o = o_raw + (size_t)r * width;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(o[j], o[j], ss);
+    ss = block_sum(ss, red);
+    const float f = rsqrtf(ss / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float x = o[j] * f * norm_w[j];
+        if (gate != nullptr) x *= gate_f(to_f32(gate[(size_t)r * ldg + j]), 0);
+        out[(size_t)r * ldo + j] = from_f32<T>(x);
     }
 }
 
@@ -854,13 +907,18 @@ static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb,
                                    const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
                                    float q_scale, float* state, size_t state_stride, T* out, int ldo, float* o_raw,
                                    const int* row_slot, const int* row_last, const int* seg_row0, int segments, int n,
-                                   int H, int G, int v_dim, cudaStream_t stream) {
+                                   int H, int G, int v_dim, int decay_mode, int gate_act, cudaStream_t stream) {
     tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS>, dim3(H, v_dim / COLS, seg_row0 != nullptr ? segments : n), dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
-               dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim);
+               dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim, decay_mode);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK) return st;
+    if (decay_mode == DECAY_CONSTANT) {
+        tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
+                   row_slot, H * v_dim);
+        return tis_check_launch("row_out_norm");
+    }
     tis_launch(delta_out_norm_kernel<T>, dim3((n * H + 3) / 4), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps,
-               out, ldo, row_slot, n, H, v_dim);
+               out, ldo, row_slot, n, H, v_dim, gate_act);
     return tis_check_launch("delta_out_norm");
 }
 
@@ -868,7 +926,8 @@ template <typename T, int DIM>
 static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const T* a_in, int lda, const T* gate, int ldg,
                              const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps,
                              float q_scale, float* state, size_t state_stride, T* out, int ldo, const int* row_slot,
-                             const int* row_last, int n, int H, int G, int k_dim, int v_dim, cudaStream_t stream) {
+                             const int* row_last, int n, int H, int G, int k_dim, int v_dim, int decay_mode, int gate_act,
+                             float* o_raw, cudaStream_t stream) {
     int threads = (v_dim + 31) / 32 * 32;
     if (threads < 128) threads = 128;                  // warps to prepare and normalise a chunk with
     size_t smem = sizeof(float) * ((size_t)DELTA_CHUNK * (3 * k_dim + 2 * v_dim + 1) + (DIM > 0 ? 0 : (size_t)k_dim * v_dim));
@@ -880,8 +939,12 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
         cudaFuncSetAttribute(delta_rule_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     tis_launch(delta_rule_kernel<T, DIM>, dim3(H, n), dim3(threads), smem, stream, qkv, ld, b_in, ldb, a_in, lda, gate, ldg,
                A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, out, ldo, row_slot, row_last, H, G,
-               k_dim, v_dim);
-    return tis_check_launch("delta_rule");
+               k_dim, v_dim, decay_mode, gate_act, decay_mode == DECAY_CONSTANT ? o_raw : (float*)nullptr);
+    int st = tis_check_launch("delta_rule");
+    if (st != TIS_OK || decay_mode != DECAY_CONSTANT) return st;
+    tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
+               row_slot, H * v_dim);
+    return tis_check_launch("row_out_norm");
 }
 
 // Whether tis_delta_rule takes the kernel that splits a head's columns over CTAs for these widths (it then needs
@@ -891,12 +954,19 @@ TIS_API int tis_delta_rule_splits(int k_dim, int v_dim) {
     switch (k_dim) { case 16: case 32: case 48: case 64: case 96: case 128: return 1; default: return 0; }
 }
 
-TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in, int ldb, const void* a_in, int lda,
-                           const void* gate, int ldg, const float* A_log, const float* dt_bias, const float* norm_w,
-                           float eps, float unit_eps, float q_scale, float* state, size_t state_stride, void* out,
-                           int ldo, float* o_raw, const int* row_slot, const int* row_last, int n, int H, int G,
-                           int k_dim, int v_dim, int narrow, const int* seg_row0, int segments, cudaStream_t stream) {
+static int matrix_state_recurrence(int dtype, const void* qkv, int ld, const void* b_in, int ldb, const void* a_in, int lda,
+                                   const void* gate, int ldg, const float* A_log, const float* dt_bias, const float* norm_w,
+                                   float eps, float unit_eps, float q_scale, float* state, size_t state_stride, void* out,
+                                   int ldo, float* o_raw, const int* row_slot, const int* row_last, int n, int H, int G,
+                                   int k_dim, int v_dim, int narrow, const int* seg_row0, int segments, int decay_mode,
+                                   int gate_act, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
+    if (decay_mode < DECAY_PER_CHANNEL || decay_mode > DECAY_CONSTANT || gate_act < 0 || gate_act > 1 ||
+        (decay_mode == DECAY_CONSTANT && o_raw == nullptr)) {
+        tis_set_error("delta_rule: decay mode %d, gate activation %d%s", decay_mode, gate_act,
+                      o_raw == nullptr ? ", no scratch for the outputs" : "");
+        return TIS_BAD_SIZE;
+    }
     if (n > 65535) {
         tis_set_error("delta_rule: %d rows in one step (at most 65535)", n);
         return TIS_BAD_SIZE;
@@ -906,7 +976,8 @@ TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in,
     if (k_dim == K)                                                                                                    \
         TIS_DISPATCH_DTYPE(dtype, T, return (launch_delta_rule_split<T, DL, LANES, COLS>((const T*)qkv, ld,            \
             (const T*)b_in, ldb, (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps,      \
-            q_scale, state, state_stride, (T*)out, ldo, o_raw, row_slot, row_last, seg_row0, segments, n, H, G, v_dim, stream)));
+            q_scale, state, state_stride, (T*)out, ldo, o_raw, row_slot, row_last, seg_row0, segments, n, H, G, v_dim,       \
+            decay_mode, gate_act, stream)));
         if (v_dim % 64 == 0 && !narrow) {               // eight lanes a column, 64 columns a CTA
             TIS_DELTA_SPLIT(32, 4, 8, 64)
             TIS_DELTA_SPLIT(64, 8, 8, 64)
@@ -936,7 +1007,8 @@ TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in,
     case D:                                                                                                            \
         TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule<T, D>((const T*)qkv, ld, (const T*)b_in, ldb,            \
             (const T*)a_in, lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state,           \
-            state_stride, (T*)out, ldo, row_slot, row_last, n, H, G, k_dim, v_dim, stream));                           \
+            state_stride, (T*)out, ldo, row_slot, row_last, n, H, G, k_dim, v_dim, decay_mode, gate_act, o_raw,        \
+            stream));                                                                                                 \
         break;
     switch (k_dim) {
         TIS_DELTA_CASE(16)
@@ -948,6 +1020,32 @@ TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in,
 #undef TIS_DELTA_CASE
     TIS_DISPATCH_DTYPE(dtype, T, return launch_delta_rule<T, 0>((const T*)qkv, ld, (const T*)b_in, ldb, (const T*)a_in,
         lda, (const T*)gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps, q_scale, state, state_stride, (T*)out, ldo,
-        row_slot, row_last, n, H, G, k_dim, v_dim, stream));
+        row_slot, row_last, n, H, G, k_dim, v_dim, decay_mode, gate_act, o_raw, stream));
     return TIS_OK;
+}
+
+// The delta rule.  decay_per_head 0: `a_in` (n, H * k_dim) and `dt_bias` (H * k_dim), a decay per head and key channel;
+// 1: `a_in` (n, H) and `dt_bias` (H), one per head.  gate_act: 0 sigmoid, 1 silu.
+TIS_API int tis_delta_rule(int dtype, const void* qkv, int ld, const void* b_in, int ldb, const void* a_in, int lda,
+                           const void* gate, int ldg, const float* A_log, const float* dt_bias, const float* norm_w,
+                           float eps, float unit_eps, float q_scale, float* state, size_t state_stride, void* out,
+                           int ldo, float* o_raw, const int* row_slot, const int* row_last, int n, int H, int G,
+                           int k_dim, int v_dim, int narrow, const int* seg_row0, int segments, int decay_per_head,
+                           int gate_act, cudaStream_t stream) {
+    return matrix_state_recurrence(dtype, qkv, ld, b_in, ldb, a_in, lda, gate, ldg, A_log, dt_bias, norm_w, eps, unit_eps,
+                                   q_scale, state, state_stride, out, ldo, o_raw, row_slot, row_last, n, H, G, k_dim, v_dim,
+                                   narrow, seg_row0, segments, decay_per_head ? DECAY_PER_HEAD : DECAY_PER_CHANNEL, gate_act,
+                                   stream);
+}
+
+// Linear attention with a constant decay per head (`decay`, H numbers): S <- decay S + silu(k) silu(v)^T, o = S^T silu(q);
+// the outputs of a row's heads together are divided by their root mean square, multiplied by `norm_w` (H * v_dim) and by
+// sigmoid(gate).  `o_raw`: n * H * v_dim floats of scratch.  The recurrence is walked by the delta rule's kernels.
+TIS_API int tis_linear_attention(int dtype, const void* qkv, int ld, const void* gate, int ldg, const float* decay,
+                                 const float* norm_w, float eps, float* state, size_t state_stride, void* out, int ldo,
+                                 float* o_raw, const int* row_slot, const int* row_last, int n, int H, int k_dim, int v_dim,
+                                 int narrow, const int* seg_row0, int segments, cudaStream_t stream) {
+    return matrix_state_recurrence(dtype, qkv, ld, nullptr, 0, nullptr, 0, gate, ldg, decay, nullptr, norm_w, eps, 0.f, 1.f,
+                                   state, state_stride, out, ldo, o_raw, row_slot, row_last, n, H, H, k_dim, v_dim, narrow,
+                                   seg_row0, segments, DECAY_CONSTANT, 0, stream);
 }

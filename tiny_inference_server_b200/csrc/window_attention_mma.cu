@@ -67,6 +67,8 @@ struct Params {
     int H, G, page_size, window;
     float scale;
     const float* r1; const float* r2;
+    const float* sink;       // per query head: exp(sink) is one more term of the softmax's denominator (null: none)
+    int v_row;               // elements from one value row of a page to the next (VD, or more when the rows are slices)
     int* fault;
     float* partial;          // [tiles][G][splits][16][VD + 2]: unnormalised out, maximum, sum (key splits over CTAs)
 };
@@ -89,7 +91,7 @@ __device__ __forceinline__ void load_tile(const Params& p, int slot, int kvh, in
     if (page >= 0) {
         const int in_page = j % p.page_size;
         const bf16* ksrc = p.k_pages + (size_t)page * p.k_page_stride + (size_t)kvh * p.k_head_stride + (size_t)in_page * KD;
-        const bf16* vsrc = p.v_pages + (size_t)page * p.v_page_stride + (size_t)kvh * p.v_head_stride + (size_t)in_page * VD;
+        const bf16* vsrc = p.v_pages + (size_t)page * p.v_page_stride + (size_t)kvh * p.v_head_stride + (size_t)in_page * p.v_row;
 #pragma unroll
         for (int c = 0; c < KC / 2; ++c) cp_async16(kd + (2 * c + half) * 8, ksrc + (2 * c + half) * 8);
 #pragma unroll
@@ -168,6 +170,12 @@ window_attention_mma_kernel(const Params p) {
 #pragma unroll
     for (int n = 0; n < VD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (p.sink != nullptr && !split_keys) {
+        // the sink's term: the running maximum starts at the sink and the running sum at 1 (in one of the four
+        // threads that share a row).  Decode rows, whose keys several warps and CTAs share, get it when those merge.
+        if (row_a) { m[0] = p.sink[head_a]; l[0] = t4 == 0 ? 1.f : 0.f; }
+        if (row_b) { m[1] = p.sink[head_b]; l[1] = t4 == 0 ? 1.f : 0.f; }
+    }
     // positions of the first and last row among this warp's packed rows
     const int w_lo = pos0 + base / gq, w_hi = min(pos0 + (base + 15) / gq, last);
     for (int kt = kt_begin; kt < ntiles; ++kt) {
@@ -309,6 +317,14 @@ window_attention_mma_kernel(const Params p) {
                 num = fmaf(src[c], f, num);
                 den = fmaf(src[VD + 1], f, den);
             }
+            if (p.sink != nullptr && blockIdx.z == 0) {        // the sink's term counts once: with the first share of the keys
+                const float sk = p.sink[kvh * gq + mrow % gq];
+                const float m2 = fmaxf(mm, sk);
+                const float f = mm == -INFINITY ? 0.f : __expf(mm - m2);
+                num *= f;
+                den = fmaf(den, f, __expf(sk - m2));
+                mm = m2;
+            }
             if (splits > 1) {                                  // this CTA's share of the keys: left for the merge kernel
                 float* dst = p.partial + ((((size_t)tile * p.G + kvh) * splits + blockIdx.z) * 16 + mrow) * PS;
                 dst[c] = num;
@@ -396,13 +412,15 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
                                      const int* block_table, int bt_stride, int num_pages, const int* positions,
                                      const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
                                      int H, int G, int page_size, int window, float scale, const float* r1,
-                                     const float* r2, int splits, float* partial, int* fault, cudaStream_t stream) {
+                                     const float* r2, int splits, float* partial, const float* sink, int v_row, int* fault,
+                                     cudaStream_t stream) {
     if (num_tiles <= 0) return TIS_OK;
     if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) {
         tis_set_error("window_attention_mma: %d key splits%s", splits, splits > 1 ? " without scratch" : "");
         return TIS_BAD_SIZE;
     }
     if (H <= 0 || G <= 0 || H % G || H / G > ROWS || page_size <= 0 || window < 0 || ldq % 8 || ldg % 2 || ldo % 2 ||
+        v_row < VD || v_row % 8 ||
         k_page_stride % 8 || k_head_stride % 8 || v_page_stride % 8 || v_head_stride % 8 ||
         ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 || ((uintptr_t)gate | (uintptr_t)out) % 4) {
         tis_set_error("window_attention_mma: %d query heads, %d kv heads, page size %d, window %d, row strides %d/%d/%d "
@@ -417,7 +435,7 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
     p.v_pages = (const bf16*)v_pages; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride;
     p.block_table = block_table; p.bt_stride = bt_stride; p.num_pages = num_pages;
     p.positions = positions; p.row_slot = row_slot; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
-    p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.scale = scale; p.r1 = r1; p.r2 = r2; p.fault = fault; p.partial = partial;
+    p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.scale = scale; p.r1 = r1; p.r2 = r2; p.fault = fault; p.partial = partial; p.sink = sink; p.v_row = v_row;
     const size_t smem = sizeof(bf16) * ((size_t)2 * KEYS * KS + 2 * KEYS * VS);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {

@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 5
+ABI_VERSION = 6
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -802,10 +802,13 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out:
     return out
 
 
-def _page_strides(pages: torch.Tensor, width: int):
-    """(page stride, head stride) of a view [pages, kv_heads, page_size, width] whose rows are dense."""
-    if pages.stride(3) != 1 or pages.stride(2) != width:
+def _page_strides(pages: torch.Tensor, width: int, free_rows: bool = False):
+    """(page stride, head stride) of a view [pages, kv_heads, page_size, width] whose rows are dense; with
+    ``free_rows`` also the stride from row to row, which may then exceed the width (a slice of wider rows)."""
+    if pages.stride(3) != 1 or (pages.stride(2) != width if not free_rows else pages.stride(2) < width):
         raise KernelError("cache pages: the rows of a kv head must lie one after the other")
+    if free_rows:
+        return ctypes.c_size_t(pages.stride(0)), ctypes.c_size_t(pages.stride(1)), int(pages.stride(2))
     return ctypes.c_size_t(pages.stride(0)), ctypes.c_size_t(pages.stride(1))
 
 
@@ -856,7 +859,7 @@ WINDOW_ATTENTION_CTAS = 2 * 148
 
 def window_attention_mma_usable(q: torch.Tensor, gate, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor) -> bool:
     k_dim, v_dim = k_pages.shape[3], v_pages.shape[3]
-    return (WINDOW_ATTENTION_MMA and q.dtype == torch.bfloat16 and k_dim % 16 == 0 and v_dim % 16 == 0
+    return (WINDOW_ATTENTION_MMA and v_pages.stride(2) % 8 == 0 and q.dtype == torch.bfloat16 and k_dim % 16 == 0 and v_dim % 16 == 0
             and 16 <= k_dim <= 256 and 16 <= v_dim <= 256 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
             and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
             and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 4 == 0))
@@ -868,11 +871,13 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                      v_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
                      num_heads: int, page_size: int, window: Optional[int], scale: float,
                      bias_slope: Optional[torch.Tensor], bias_rate: Optional[torch.Tensor], fault: torch.Tensor,
-                     step=None) -> torch.Tensor:
+                     step=None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's rows over the paged cache with keys and values of any widths:
     ``score = q . k * scale - bias_slope[h] * ln(1 + bias_rate[h] * distance)``, softmax over the keys
     ``max(0, p - window + 1) .. p``, the result times ``sigmoid(gate)`` element by element.  ``q`` (n, H * k_dim),
-    ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free.
+    ``gate`` (n, H * v_dim) or None, ``out`` (n, H * v_dim); row strides free.  ``sink`` (H,) float32: the softmax's
+    denominator of head h also holds ``exp(sink[h])`` (unscaled; it has no value).  The value rows may be a slice of
+    wider rows (``v_pages`` with a row stride above its width, for instance the first elements of the key rows).
 
     float32, and widths that are not multiples of 16: a CUDA-core kernel, a CTA per row and head.  bfloat16 inside
     a step (``step`` given, with the tiles of ``kernels.window_plan``): the tensor-core kernel, a CTA per tile of rows
@@ -881,7 +886,7 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     n = q.shape[0]
     kv_heads, k_dim, v_dim = k_pages.shape[1], k_pages.shape[3], v_pages.shape[3]
     kps, khs = _page_strides(k_pages, k_dim)
-    vps, vhs = _page_strides(v_pages, v_dim)
+    vps, vhs, v_row = _page_strides(v_pages, v_dim, free_rows=True)
     if step is not None and num_heads // kv_heads <= 64 and window_attention_mma_usable(q, gate, out, k_pages, v_pages):
         from . import window_plan
         row0, rows, count = step.plan(window_plan.planner(num_heads // kv_heads))
@@ -905,16 +910,19 @@ def window_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
                                              _p(block_table), block_table.stride(0), k_pages.shape[0], _p(positions),
                                              _p(row_slot), _p(row0), _p(rows), count, num_heads, kv_heads, page_size,
                                              int(window or 0), _f(scale), _p(bias_slope), _p(bias_rate), splits, _p(partial),
-                                             _p(fault), _stream()), wlib)
+                                             _p(sink), v_row, _p(fault), _stream()), wlib)
         return out
     calls["window_attention"] += 1
     _check(lib.tis_window_attention(_dt(q), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                     _p(out), out.stride(0), _p(k_pages), kps, khs, _p(v_pages), vps, vhs, _p(block_table),
                                     block_table.stride(0), k_pages.shape[0], _p(positions), _p(row_slot), n, num_heads,
                                     kv_heads, k_dim, v_dim, page_size, int(window or 0), _f(scale), _p(bias_slope),
-                                    _p(bias_rate), _p(fault), _stream()), lib)
+                                    _p(bias_rate), _p(sink), v_row, _p(fault), _stream()), lib)
     return out
 
+
+#: what a mixer's gate does to the projection it is made from
+GATE_ACTS = {"sigmoid": 0, "silu": 1}
 
 #: CTAs of 64 columns from which the delta rule keeps them (fewer: 16 columns a CTA, four times as many CTAs)
 DELTA_WIDE_MIN_CTAS = 2 * 148
@@ -924,13 +932,14 @@ def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, ga
                a_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float, unit_eps: float,
                q_scale: float, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor,
                num_heads: int, qk_heads: int, k_dim: int, v_dim: int, requests: Optional[int] = None,
-               segments=None) -> torch.Tensor:
-    """The delta rule with a decay per head and key channel over the rows of every request, from and into the
+               segments=None, decay_per_head: bool = False, gate_act: str = "sigmoid") -> torch.Tensor:
+    """The delta rule with a decay per head and key channel (``decay_per_head``: one per head; ``decay_in`` is then
+    (n, H) and ``dt_bias`` (H,)) over the rows of every request, from and into the
     requests' states ``state`` (slots, H, k_dim, v_dim) float32 (a view with a free slot stride).  A row of ``qkv``:
     queries and keys of ``qk_heads`` heads, values of ``num_heads`` heads.  Per head: q and k to unit length
     (``unit_eps`` inside the root; q times ``q_scale``), beta = sigmoid(``beta``), decay = exp(-exp(a_log) *
     softplus(``decay_in`` + dt_bias)) per key channel; S <- decay S; u = beta (v - S^T k); S <- S + k u^T;
-    o = S^T q; out = o / rms(o) * norm_weight * sigmoid(gate).  ``requests``: how many requests the step holds, if
+    o = S^T q; out = o / rms(o) * norm_weight * act(gate), act = ``gate_act`` (``GATE_ACTS``).  ``requests``: how many requests the step holds, if
     the caller knows (few requests: a head's columns are shared out over more CTAs).  ``segments``: (first rows of
     the step's requests as an int32 device tensor, their number), from ``kernels.segment_plan``: the kernel then
     launches CTAs for the requests only, not for every row."""
@@ -949,7 +958,114 @@ def delta_rule(qkv: torch.Tensor, beta: torch.Tensor, decay_in: torch.Tensor, ga
                               _f(eps), _f(unit_eps), _f(q_scale), _p(state), ctypes.c_size_t(state.stride(0)), _p(out),
                               out.stride(0), _p(raw), _p(row_slot), _p(row_last), n, num_heads, qk_heads, k_dim, v_dim,
                               int(narrow), _p(segments[0] if segments is not None else None),
-                              int(segments[1]) if segments is not None else 0, _stream()), lib)
+                              int(segments[1]) if segments is not None else 0, int(bool(decay_per_head)),
+                              GATE_ACTS[gate_act], _stream()), lib)
+    return out
+
+
+def linear_attention(qkv: torch.Tensor, gate: Optional[torch.Tensor], decay: torch.Tensor, norm_weight: torch.Tensor,
+                     eps: float, state: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor,
+                     num_heads: int, k_dim: int, v_dim: int, requests: Optional[int] = None, segments=None) -> torch.Tensor:
+    """Linear attention with a constant decay per head over the rows of every request, from and into the requests'
+    states ``state`` (slots, H, k_dim, v_dim) float32 (a view with a free slot stride).  A row of ``qkv``: queries and
+    keys of H heads (k_dim each), values of H heads (v_dim each), all before their activation.  q = silu(q),
+    k = silu(k), v = silu(v); S <- decay[head] S + k v^T; o = S^T q; the row's outputs of all heads together are divided
+    by their root mean square (eps inside the root), multiplied by ``norm_weight`` (H * v_dim) and by sigmoid(gate).
+    ``requests`` and ``segments`` as for ``delta_rule``: the same kernels walk the recurrence."""
+    lib = library()
+    n = qkv.shape[0]
+    narrow = requests is not None and requests * num_heads * max(1, v_dim // 64) < DELTA_WIDE_MIN_CTAS
+    raw = torch.empty((n, num_heads * v_dim), dtype=torch.float32, device=qkv.device)
+    global launches
+    launches += 1
+    _check(lib.tis_linear_attention(_dt(qkv), _p(qkv), qkv.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                    _p(decay), _p(norm_weight), _f(eps), _p(state), ctypes.c_size_t(state.stride(0)),
+                                    _p(out), out.stride(0), _p(raw), _p(row_slot), _p(row_last), n, num_heads, k_dim, v_dim,
+                                    int(narrow), _p(segments[0] if segments is not None else None),
+                                    int(segments[1]) if segments is not None else 0, _stream()), lib)
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, dkv_at: int, num_heads: int, flat_dim: int, rot_dim: int, rank: int,
+                   c_weight: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor, q_out: torch.Tensor,
+                   k_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor,
+                   page_size: int, fault: torch.Tensor) -> None:
+    """Between the projections and the cache of attention over compressed keys and values.  A row of ``proj`` holds,
+    per head, ``flat_dim + rot_dim`` query elements, and from column ``dkv_at`` on ``rank + rot_dim`` elements of the
+    compressed projection.  The first ``rank`` of those, divided by their root mean square (eps inside the root) and
+    multiplied by ``c_weight``, and the last ``rot_dim``, rotated by the row's position (pairs (i, i + rot_dim / 2),
+    tables ``cos, sin`` [positions, rot_dim / 2] float32), are written as the row ``[c | rotated slice]`` of the
+    position's page in ``k_pages`` [pages, 1, page_size, rank + rot_dim].  The last ``rot_dim`` elements of every
+    head's query, rotated the same way, go to ``q_out`` (n, H * (rank + rot_dim)) behind the ``rank`` places that
+    the caller fills.  Everything is computed in 32-bit."""
+    lib = library()
+    n = proj.shape[0]
+    if k_pages.shape[1] != 1 or k_pages.shape[3] != rank + rot_dim or cos.shape[1] * 2 != rot_dim:
+        raise KernelError("latent_prepare: the cache rows or the rotation tables do not fit the sizes")
+    kps, _ = _page_strides(k_pages, rank + rot_dim)
+    _check(lib.tis_latent_prepare(_dt(proj), _p(proj), proj.stride(0), dkv_at, num_heads, flat_dim, rot_dim, rank,
+                                  _p(c_weight), _f(eps), _p(cos), _p(sin), cos.shape[0], _p(q_out), q_out.stride(0),
+                                  _p(k_pages), kps, page_size, k_pages.shape[0], _p(block_table), block_table.stride(0),
+                                  _p(positions), _p(row_slot), _p(fault), n, _stream()), lib)
+
+
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[r, h] = a[r, h] @ w[h]`` for every head h: ``a`` (n, H, K), ``w`` (H, K, N), ``out`` (n, H, N), the first
+    two with free row and head strides.  A batched library product (float32 means true float32)."""
+    if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
+    calls["gemm_heads"] += 1
+    out.copy_(torch.bmm(a.transpose(0, 1), w).transpose(0, 1))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# routed experts
+# ---------------------------------------------------------------------------------------
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
+              w_shared_gate: Optional[torch.Tensor], groups: int, keep: int, top: int, weight_eps: float = 1e-20):
+    """The router of a mixture of experts, a row at a time, in 32-bit: ``s = sigmoid(w_router x)`` (E experts);
+    choosing scores ``s + correction``; with ``groups`` > 0 only the experts of the ``keep`` groups (of E / groups
+    neighbours) with the largest sum of their two best choosing scores can be chosen; the ``top`` largest choosing
+    scores win (the lower index on a tie); weights ``s`` of the chosen over their sum (+ ``weight_eps``).  Returns
+    (chosen (n, top) int32, weights (n, top) float32, sigmoid(w_shared_gate . x) (n,) float32 or None)."""
+    lib = library()
+    n, d = x.shape
+    experts = w_router.shape[0]
+    chosen = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    shared = torch.empty((n,), dtype=torch.float32, device=x.device) if w_shared_gate is not None else None
+    _check(lib.tis_moe_route(_dt(x), _p(x), x.stride(0), _p(w_router), _p(correction), _p(w_shared_gate), n, d, experts,
+                             int(groups), int(keep), int(top), _f(weight_eps), _p(chosen), _p(weights), _p(shared),
+                             _stream()), lib)
+    return chosen, weights, shared
+
+
+def moe_gate_up(x: torch.Tensor, chosen: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``hidden[r * top + k] = silu(Wg[e] x[r]) * (Wu[e] x[r])`` with ``e = chosen[r, k]``: ``w_gate_up`` (E, 2, F, d)
+    holds every expert's gate and up matrices (out, in); the result is (n * top, F) in the dtype of ``x``."""
+    lib = library()
+    n, d = x.shape
+    top = chosen.shape[1]
+    experts, _, hidden, _ = w_gate_up.shape
+    out = torch.empty((n * top, hidden), dtype=x.dtype, device=x.device)
+    _check(lib.tis_moe_gate_up(_dt(x), _p(x), x.stride(0), _p(chosen), _p(w_gate_up), _p(out), n, d, top, experts, hidden,
+                               _stream()), lib)
+    return out
+
+
+def moe_down(hidden: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_down: torch.Tensor,
+             shared: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor]) -> torch.Tensor:
+    """``out[r] = sum_k weights[r, k] * Wd[chosen[r, k]] hidden[r * top + k] (+ shared_gate[r] * shared[r])``:
+    ``w_down`` (E, d, F) (out, in), ``hidden`` (n * top, F), ``shared`` (n, d) or None; the result is (n, d)."""
+    lib = library()
+    n, top = chosen.shape
+    experts, d, f = w_down.shape
+    out = torch.empty((n, d), dtype=hidden.dtype, device=hidden.device)
+    _check(lib.tis_moe_down(_dt(hidden), _p(hidden), _p(chosen), _p(weights), _p(w_down), _p(shared),
+                            shared.stride(0) if shared is not None else 0, _p(shared_gate), _p(out), n, d, top, experts, f,
+                            _stream()), lib)
     return out
 
 

@@ -4,16 +4,19 @@ from .base import (BuildContext, FeedForward, KVSpec, LayerBinding, Mixer, Norm,
                    StateSpec, WeightSpec)
 from .stream import ResidualStream
 from .norms import RMSNormL2, RMSNormMeanEps, RMSNormOnePlus
-from .positions import RotaryHalf, RotaryInterleaved
+from .positions import RotaryHalf, RotaryInterleaved, RotaryRescaled
 from .attention import GqaAttention
-from .feed_forward import ClampedGLU, SwiGLU
+from .feed_forward import ClampedGLU, RoutedExperts, SwiGLU
 from .short_conv import CausalConv
 from .window_attention import BiasedWindowAttention, ValueShare
-from .delta_rule import ChannelDeltaRule
+from .delta_rule import ChannelDeltaRule, HeadDecayDeltaRule
+from .linear_attention import DecayLinearAttention
+from .latent_attention import LatentAttention
 from .block import Block
 from .embedding import Embedding, LMHead
 
 __all__ = ["BuildContext", "FeedForward", "KVSpec", "LayerBinding", "Mixer", "Norm", "Part",
            "PositionEncoding", "StateSpec", "WeightSpec", "ResidualStream", "RMSNormL2", "RMSNormMeanEps", "RMSNormOnePlus", "ClampedGLU", "CausalConv",
-           "BiasedWindowAttention", "ValueShare", "ChannelDeltaRule", "RotaryHalf",
+           "BiasedWindowAttention", "ValueShare", "ChannelDeltaRule", "HeadDecayDeltaRule", "DecayLinearAttention", "LatentAttention", "RoutedExperts",
+           "RotaryRescaled", "RotaryHalf",
            "RotaryInterleaved", "GqaAttention", "SwiGLU", "Block", "Embedding", "LMHead"]

@@ -21,10 +21,12 @@ class SwiGLU(FeedForward):
     accepts_scaled_rows = True
     fuses_residual = True
 
-    def __init__(self, width: int, hidden: int, prefix: str = "", names: Optional[Dict[str, str]] = None):
+    def __init__(self, width: int, hidden: int, prefix: str = "", names: Optional[Dict[str, str]] = None,
+                 stored_out_in: bool = False):
         super().__init__(prefix)
         self.width = width
         self.hidden = hidden
+        self.stored_out_in = stored_out_in        # the three matrices are stored (out, in) instead of (in, out)
         self.names = {"gate": "swig.linear1.weight", "up": "swig.linear2.weight", "down": "fc.weight"}
         if names:
             self.names.update(names)
@@ -37,20 +39,23 @@ class SwiGLU(FeedForward):
         return cls(cfg.hidden_size, cfg.ffn_hidden, prefix=prefix)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {
-            self.names["gate"]: WeightSpec((self.width, self.hidden)),
-            self.names["up"]: WeightSpec((self.width, self.hidden)),
-            self.names["down"]: WeightSpec((self.hidden, self.width)),
-        }
+        wide, tall = (self.width, self.hidden), (self.hidden, self.width)
+        if self.stored_out_in:
+            wide, tall = tall, wide
+        return {self.names["gate"]: WeightSpec(wide), self.names["up"]: WeightSpec(wide),
+                self.names["down"]: WeightSpec(tall)}
 
     def load(self, tensors, ctx: BuildContext) -> None:
         gate = tensors[self.prefix + self.names["gate"]]
         up = tensors[self.prefix + self.names["up"]]
+        down = tensors[self.prefix + self.names["down"]]
+        if self.stored_out_in:
+            gate, up, down = gate.t(), up.t(), down.t()
         self.block = 32 if self.hidden % 32 == 0 else self.hidden
         nb = self.hidden // self.block
         both = torch.stack([gate.reshape(self.width, nb, self.block), up.reshape(self.width, nb, self.block)], dim=2)
         self.w_gate_up = both.reshape(self.width, 2 * self.hidden).to(device=ctx.device, dtype=ctx.dtype).contiguous()
-        self.w_down = tensors[self.prefix + self.names["down"]].to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        self.w_down = down.to(device=ctx.device, dtype=ctx.dtype).contiguous()
 
     def forward(self, x, step=None, residual=None):
         h = ops.gemm_swiglu(x, self.w_gate_up, self.hidden, self.block)
@@ -104,5 +109,81 @@ class ClampedGLU(FeedForward):
         return ops.gemm(y, self.w_down)
 
 
+class RoutedExperts(FeedForward):
+    """A mixture of ``experts`` small gated units ``W_down (silu(W_gate h) * (W_up h))`` (no biases), of which every
+    token uses ``top``:
+
+    * router: ``z = W_router h`` and ``s = sigmoid(z)`` in 32-bit; an expert is *chosen* by ``s + correction`` and
+      *weighted* by ``s``;
+    * ``groups`` > 0: the experts form that many equal groups of neighbours; a group's strength is the sum of its
+      two largest choosing scores, and only the experts of the ``keep`` strongest groups can be chosen;
+    * the ``top`` experts with the largest choosing scores are taken (the lower index on a tie); their weights are
+      their ``s`` divided by the sum of those (+ ``weight_eps``);
+    * ``shared_hidden`` > 0: one more unit of that hidden size runs for every token and is added times
+      ``sigmoid(w_sg . h)``, one number per token.
+
+    Tensor names below the prefix: ``e<i>.gate, e<i>.up, e<i>.down``, ``router``, ``correction``, ``shared.gate,
+    shared.up, shared.down, shared.sg`` (matrices stored (out, in)).  On the device the experts' matrices are stacked:
+    gate and up ``(experts, 2, hidden, width)``, down ``(experts, width, hidden)``; the kernels find an expert's rows
+    from the token's choice, so nothing is sorted or gathered on the host."""
+
+    WEIGHT_EPS = 1e-20
+
+    def __init__(self, width: int, hidden: int, experts: int, top: int, groups: int = 0, keep: int = 0,
+                 shared_hidden: int = 0, prefix: str = ""):
+        super().__init__(prefix)
+        if groups and (experts % groups or not (0 < keep <= groups)):
+            raise ValueError(f"{experts} experts in {groups} groups, {keep} kept")
+        if top > (experts // groups * keep if groups else experts):
+            raise ValueError(f"top {top} exceeds the experts that can be chosen")
+        self.width, self.hidden, self.experts, self.top = width, hidden, experts, top
+        self.groups, self.keep, self.shared_hidden = groups, keep, shared_hidden
+        self.shared = SwiGLU(width, shared_hidden, prefix=prefix + "shared.", stored_out_in=True,
+                             names={"gate": "gate", "up": "up", "down": "down"}) if shared_hidden else None
+        self.w_gate_up = self.w_down = self.w_router = self.correction = self.w_shared_gate = None
+
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int):
+        f = cfg.layers[layer_index]["mlp"]
+        r = f["router"]
+        g = r.get("groups") or {}
+        s = f.get("shared") or {}
+        return cls(cfg.hidden_size, f["expert"]["ff"], r["experts"], r["top"], g.get("count", 0), g.get("keep", 0),
+                   s.get("ff", 0), prefix=prefix)
+
+    def children(self):
+        return (self.shared,) if self.shared is not None else ()
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {"router": WeightSpec((self.experts, self.width)), "correction": WeightSpec((self.experts,))}
+        for e in range(self.experts):
+            specs[f"e{e}.gate"] = WeightSpec((self.hidden, self.width))
+            specs[f"e{e}.up"] = WeightSpec((self.hidden, self.width))
+            specs[f"e{e}.down"] = WeightSpec((self.width, self.hidden))
+        if self.shared is not None:
+            specs["shared.sg"] = WeightSpec((1, self.width))
+        return specs
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        p = self.prefix
+        dev = dict(device=ctx.device, dtype=ctx.dtype)
+        f32 = dict(device=ctx.device, dtype=torch.float32)
+        gu = torch.stack([torch.stack([tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"]]) for e in range(self.experts)])
+        self.w_gate_up = gu.to(**dev).contiguous()
+        self.w_down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.experts)]).to(**dev).contiguous()
+        self.w_router = tensors[p + "router"].to(**f32).contiguous()
+        self.correction = tensors[p + "correction"].to(**f32).contiguous()
+        if self.shared is not None:
+            self.w_shared_gate = tensors[p + "shared.sg"].to(**f32).reshape(-1).contiguous()
+
+    def forward(self, x, step=None):
+        chosen, weights, shared_gate = ops.moe_route(x, self.w_router, self.correction, self.w_shared_gate, self.groups,
+                                                     self.keep, self.top, self.WEIGHT_EPS)
+        hidden = ops.moe_gate_up(x, chosen, self.w_gate_up)
+        shared = self.shared.forward(x, step) if self.shared is not None else None
+        return ops.moe_down(hidden, chosen, weights, self.w_down, shared, shared_gate)
+
+
 register_part("ffn", "swiglu", SwiGLU)
+register_part("ffn", "routed_experts", RoutedExperts)
 register_part("ffn", "clamped_glu", ClampedGLU)

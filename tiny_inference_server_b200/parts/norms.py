@@ -48,14 +48,17 @@ class RMSNormL2(Norm):
 
 class RMSNormMeanEps(Norm):
     """``y = x / sqrt(mean(x^2) + eps) * (offset + w)`` in float32, eps inside the root.  ``offset`` 1: the
-    stored tensor is the weight's distance from one; 0: it is the weight."""
+    stored tensor is the weight's distance from one; 0: it is the weight.  ``keep_f32``: the result is float32
+    whatever the compute dtype."""
 
-    def __init__(self, width: int, eps: float, prefix: str = "", weight_name: str = "weight", offset: float = 0.0):
+    def __init__(self, width: int, eps: float, prefix: str = "", weight_name: str = "weight", offset: float = 0.0,
+                 keep_f32: bool = False):
         super().__init__(prefix)
         self.width = width
         self.eps = float(eps)
         self.weight_name = weight_name
         self.offset = float(offset)
+        self.keep_f32 = keep_f32                  # the result stays in 32-bit (a norm that makes the residual stream)
         self.scale: Optional[torch.Tensor] = None
         self.out_dtype = torch.float32
 
@@ -69,7 +72,7 @@ class RMSNormMeanEps(Norm):
     def load(self, tensors, ctx: BuildContext) -> None:
         w = tensors[self.prefix + self.weight_name].to(device=ctx.device, dtype=torch.float32)
         self.scale = (w + self.offset).contiguous()
-        self.out_dtype = ctx.dtype
+        self.out_dtype = torch.float32 if self.keep_f32 else ctx.dtype
 
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)

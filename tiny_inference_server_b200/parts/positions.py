@@ -69,5 +69,47 @@ class RotaryInterleaved(RotaryHalf):
         super().__init__(head_dim, theta, max_positions, rotary_dim, interleaved=True, prefix=prefix)
 
 
+class RotaryRescaled(RotaryHalf):
+    """``RotaryHalf`` whose frequencies are rescaled for contexts longer than the ``original`` one a model was
+    trained on.  With f_i = theta^(-2i/rot) and c(r) = rot * ln(original / (2 pi r)) / (2 ln theta) — the channel
+    whose wave turns r times over the original context — channels up to lo = max(floor(c(fast)), 0) keep f_i,
+    channels from hi = min(ceil(c(slow)), rot - 1) on use f_i / factor, and between them the two are blended with the
+    weight clamp((i - lo) / max(hi - lo, 0.001), 0, 1); cosines and sines are multiplied by 0.1 ln(factor) + 1.
+    ``scaling`` None: plain frequencies, magnitude 1.  The tables are formed in float64 on the host."""
+
+    def __init__(self, head_dim: int, theta: float, max_positions: int, scaling: Optional[dict] = None,
+                 rotary_dim: Optional[int] = None, prefix: str = ""):
+        super().__init__(head_dim, theta, max_positions, rotary_dim, interleaved=False, prefix=prefix)
+        self.scaling = dict(scaling) if scaling else None
+
+    def frequencies(self):
+        """(float64 frequencies (rot/2,), magnitude)."""
+        import math
+        rot = self.rotary_dim
+        i = torch.arange(0, rot // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / rot)
+        sc = self.scaling
+        if not sc:
+            return f, 1.0
+        factor, original = float(sc["factor"]), float(sc["original"])
+
+        def channel(turns: float) -> float:
+            return rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(channel(float(sc["fast"]))), 0)
+        hi = min(math.ceil(channel(float(sc["slow"]))), rot - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+    def tables(self):
+        f, magnitude = self.frequencies()
+        ang = torch.outer(torch.arange(self.max_positions, dtype=torch.float64), f)
+        return (torch.cos(ang) * magnitude).to(torch.float32), (torch.sin(ang) * magnitude).to(torch.float32)
+
+    def fused_rotary(self):
+        return None
+
+
 register_part("position", "rope_half", RotaryHalf)
+register_part("position", "rope_rescaled", RotaryRescaled)
 register_part("position", "rope_interleaved", RotaryInterleaved)
