@@ -299,6 +299,76 @@ def kefisun_config(width, heads, kv_heads, ffn, vocab, layers, window):
                          "mlp": dict(ff)} for i in range(layers)])
 
 
+def mizidra_config(width, heads, kv_heads, ffn, vocab, layers, rank=128, rot=64, experts=16, top=3):
+    """A Mizidra model with the layer sizes of a member of the GQA family: per four layers one of the delta rule, two
+    of attention over compressed keys and values and one of linear attention, keys and values of 128 elements; every
+    layer with routed experts of which ``top`` of ffn / (top + 1) hidden elements and a shared one of the same size
+    run a token, so that a token meets as many feed-forward weights as in the dense model."""
+    fe = max(32, ffn // (top + 1) // 32 * 32)
+    delta = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4}
+    latent = {"heads": heads, "dim": 64, "rot_dim": rot, "vdim": 128, "kv_rank": rank, "scale": (64 + rot) ** -0.5,
+              "rot": {"base": 1e6, "dims": rot, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    linear = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(5 + i % 4) for i in range(heads)]}
+    kinds = [("delta", delta), ("latent_attention", latent), ("lightning", linear), ("latent_attention", latent)]
+    ff = {"kind": "moe", "expert": {"ff": fe}, "shared": {"ff": fe},
+          "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
+    return dict(architecture="Mizidra", vocab=vocab, width=width, norm={"eps": 1e-6}, max_context=8192,
+                layers=[{"type": kinds[i % 4][0], "mixer": dict(kinds[i % 4][1]), "mlp": json.loads(json.dumps(ff))}
+                        for i in range(layers)])
+
+
+def compare_mizidra(args):
+    """``--compare mizidra``: prefill and decode of the Mizidra architecture beside the Kefisun architecture (the
+    closest earlier one: recurrent layers beside attention layers) and the rotary GQA model at equal layer sizes, and
+    its kernels beside the like kernels of those.  One JSON line; the default run is untouched."""
+    import gc
+    import types
+    import torch
+    from tiny_inference_server_b200.kernels import microbench, ops
+    from tiny_inference_server_b200.sampling import Sampler
+    pk = peaks()
+    count_ops = lambda: ops.launches  # noqa: E731
+    window, ctx, layers = 4096, 4096, 8
+    result = {"compare": "mizidra", "dtype": "bf16", "data": "synthetic", "layers": layers, "context": ctx, "peaks": pk,
+              "sizes": {}}
+    for name in [x for x in args.compare_sizes.split(",") if x]:
+        base = SIZES[name][0]
+        twin = dict(base, num_layers=layers, num_mtp_heads=0, max_context=8192, tie_word_embeddings=True)
+        size = (base["hidden_size"], base["num_heads"], base["num_kv_heads"], base["ffn_hidden"], base["vocab_size"], layers)
+        point = {}
+        for label, cfg_dict in (("mizidra", mizidra_config(*size)), ("kefisun", kefisun_config(*size, window)), ("gqa", twin)):
+            runner = None
+            try:
+                _, runner = build_runner(cfg_dict, ctx, 8, mtp=False)
+                steps = max(8, args.steps // 2)
+                r = {}
+                for b in (1, 8):
+                    ms, launches = decode_run(runner, b, ctx - steps - args.warmup - 2, steps, args.warmup, Sampler, count_ops)
+                    r[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    r[f"decode_b{b}_ms"] = round(ms, 4)
+                    r[f"decode_b{b}_launches"] = round(launches, 1)
+                best, first = prefill_run(runner, PREFILL_TOKENS, reps=2)
+                r["prefill_tok_s"] = round(PREFILL_TOKENS / (best * 1e-3), 1)
+                r["prefill_ms"] = round(best, 3)
+                r["prefill_first_run_ms"] = round(first, 3)
+                point[label] = r
+            except Exception as e:                       # noqa: BLE001
+                point[label] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            del runner
+            gc.collect()
+            torch.cuda.empty_cache()
+        margs = types.SimpleNamespace(width=base["hidden_size"], ffn=base["ffn_hidden"], heads=base["num_heads"],
+                                      kv_heads=base["num_kv_heads"], head_dim=128, page_size=PAGE, tokens=PREFILL_TOKENS, batch=8,
+                                      context=ctx, rank=128, rot=64, experts=16, top=3)
+        try:
+            point["kernels"] = microbench.latent_linear_routed(margs)
+        except Exception as e:                           # noqa: BLE001
+            point["kernels"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        result["sizes"][name] = point
+    print(json.dumps(result))
+    return 0
+
+
 def compare_kefisun(args):
     """``--compare kefisun``: prefill and decode of the Kefisun architecture beside the rotary GQA model at equal
     layer sizes (same width, heads, feed-forward, vocabulary, number of layers, and the same window of keys), and
@@ -444,7 +514,7 @@ def main(argv=None):
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, other contexts, MTP heads and prefill")
     ap.add_argument("--sizes", default="3b,8b", help="larger members of the family to measure too (3b, 8b; '' = none)")
-    ap.add_argument("--compare", default=None, choices=["kefisun"],
+    ap.add_argument("--compare", default=None, choices=["kefisun", "mizidra"],
                     help="instead of the default run: another architecture beside the GQA model at equal layer sizes")
     ap.add_argument("--compare-sizes", default="0.9b,3b", help="with --compare: whose layer sizes (0.9b, 3b, 8b)")
     args = ap.parse_args(argv)
@@ -453,6 +523,9 @@ def main(argv=None):
     if args.compare == "kefisun":
         args.warmup = max(args.warmup, 3)
         return compare_kefisun(args)
+    if args.compare == "mizidra":
+        args.warmup = max(args.warmup, 3)
+        return compare_mizidra(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -134,6 +134,18 @@ def delta_mixer(h, W, p, m, eps):
     return o.reshape(L, H * vdim) @ W[p + "o"].T
 
 
+def attend_with_sink(q, k, v, scale, sink):
+    """q, k (L, H, dk), v (L, H, dv), sink (H,) or None: causal softmax attention whose denominator holds one more
+    term per head, exp(sink), that has no key and no value (it is not scaled)."""
+    L, H = q.shape[0], q.shape[1]
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale
+    s = s.masked_fill(torch.triu(torch.ones(L, L, dtype=torch.bool), 1), -math.inf)
+    if sink is not None:
+        s = torch.cat([s, sink.view(H, 1, 1).expand(H, L, 1).to(s.dtype)], dim=-1)
+    w = torch.softmax(s, dim=-1)[..., :L]
+    return torch.einsum("hij,jhd->ihd", w, v)
+
+
 def latent_attention_mixer(h, W, p, m, eps, positions=None):
     L = h.shape[0]
     H, dim, rd, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
@@ -145,12 +157,9 @@ def latent_attention_mixer(h, W, p, m, eps, positions=None):
     k_rot = rotate(down[:, rank:], pos, m["rot"])                                  # (L, rd), the same for every head
     k_flat = (c @ W[p + "uk"].T).view(L, H, dim)
     v = (c @ W[p + "uv"].T).view(L, H, vdim)
-    s = (torch.einsum("ihd,jhd->hij", q_flat, k_flat) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * m["scale"]
-    s = s.masked_fill(torch.triu(torch.ones(L, L, dtype=torch.bool), 1), -math.inf)
-    # one more term in the denominator: exp(sink) with no key and no value behind it
-    s = torch.cat([s, W[p + "sink"].view(H, 1, 1).expand(H, L, 1)], dim=-1)
-    w = torch.softmax(s, dim=-1)[..., :L]
-    o = torch.einsum("hij,jhd->ihd", w, v)
+    q_all = torch.cat([q_flat, q_rot], dim=-1)
+    k_all = torch.cat([k_flat, k_rot[:, None, :].expand(L, H, rd)], dim=-1)
+    o = attend_with_sink(q_all, k_all, v, m["scale"], W[p + "sink"])
     return o.reshape(L, H * vdim) @ W[p + "o"].T
 
 

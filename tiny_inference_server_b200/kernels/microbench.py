@@ -9,6 +9,8 @@
     python -m tiny_inference_server_b200.kernels.microbench sampling --rows 8 --vocab 49152
     python -m tiny_inference_server_b200.kernels.microbench seqmix --window 1024   (windowed attention, short
         convolution, delta rule and gating, each beside the like kernel of the rotary GQA model)
+    python -m tiny_inference_server_b200.kernels.microbench latent-linear-routed   (attention over compressed keys
+        and values, recurrences with a decay per head, routed experts, each beside the like kernel of an earlier model)
     python -m tiny_inference_server_b200.kernels.microbench all
 
 ``--reps N --no-timing`` launches the kernel N times and exits (a profiler attaches to that);
@@ -296,6 +298,142 @@ def seqmix(args, hbm_gbs=None, tflops=None):
 
 
 
+def latent_linear_routed(args):
+    """The kernels of attention over compressed keys and values, of the recurrences with one decay per head (the delta
+    rule, linear attention) and of routed experts, each beside the kernel of an earlier architecture of this engine
+    that does the like work at equal sizes (``None``: there is none).  Sizes: ``heads`` heads; the recurrences with
+    keys and values of ``head_dim``; attention with ``rank`` compressed elements and ``rot`` rotated ones a token;
+    ``experts`` experts of ``ffn / (top + 1)`` hidden elements of which ``top`` run a token.  Returns {name: {us,
+    rate, unit, like_us, like_rate}}."""
+    dev = "cuda"
+    d, F, H, G, hd, page = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.page_size
+    n, B, ctx = args.tokens, args.batch, args.context
+    rank, rot, E, top = args.rank, args.rot, args.experts, args.top
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    i32 = dict(device=dev, dtype=torch.int32)
+    fault = torch.zeros(4, **i32)
+    out = {}
+
+    def put(name, us, work, unit, like_us=None, like_work=None):
+        e = {"us": round(us, 2), "rate": round(work / us / 1e3, 1) if unit == "GB/s" else round(work / us / 1e6, 1), "unit": unit}
+        if like_us is not None:
+            lw = work if like_work is None else like_work
+            e["like_us"] = round(like_us, 2)
+            e["like_rate"] = round(lw / like_us / 1e3, 1) if unit == "GB/s" else round(lw / like_us / 1e6, 1)
+        out[name] = e
+        like = f"   like kernel {e['like_us']:9.2f} us {e['like_rate']:9.1f} {unit}" if like_us is not None else ""
+        print(f"{name:44s} {e['us']:9.2f} us {e['rate']:9.1f} {unit}{like}")
+
+    # ---- attention over a prompt portion of n rows from position 0: one kv head of rank + rot elements a key, whose first
+    # rank elements are the value, H query heads, a sink; beside windowed attention with G kv heads of head_dim
+    row = rank + rot
+    num_pages = (n + page - 1) // page
+    pages = [torch.randn(num_pages, 1, page, row, **bf) for _ in range(2)]
+    like_planes = [torch.randn(num_pages, 2, G, page, hd, **bf) for _ in range(2)]
+    table = torch.arange(num_pages, **i32).reshape(1, num_pages).contiguous()
+    pos, slot = torch.arange(n, **i32), torch.zeros(n, **i32)
+    last = torch.full((n,), n - 1, **i32)
+    q = torch.randn(n, H * row, **bf)
+    lat = torch.empty(n, H * rank, **bf)
+    sink = torch.zeros(H, device=dev)
+    step = _PortionStep(pos, slot)
+    pairs = n * (n + 1) // 2
+    t_new = _graph_time(lambda i: ops.window_attention(q, None, lat, pages[i % 2], pages[i % 2][..., :rank], table, pos, slot, H,
+                                                       page, None, row ** -0.5, None, None, fault, step, sink=sink), 6)
+    ql = torch.randn(n, H * hd, **bf)
+    ol = torch.empty(n, H * hd, **bf)
+    r1, r2 = torch.rand(H, device=dev) + 0.2, torch.rand(H, device=dev) + 0.1
+    t_like = _graph_time(lambda i: ops.window_attention(ql, None, ol, like_planes[i % 2][:, 0], like_planes[i % 2][:, 1], table,
+                                                        pos, slot, H, page, None, hd ** -0.5, r1, r2, fault, step), 6)
+    put(f"latent attention, {n} rows", t_new, 2.0 * H * (row + rank) * pairs, "TFLOP/s", t_like, 4.0 * H * hd * pairs)
+    # ---- B decode rows at position ctx - 1
+    pages_per = (ctx + page - 1) // page
+    n_bufs = max(2, min(12, (300 << 20) // max(1, B * ctx * row * 2)))
+    pages = [torch.randn(B * pages_per, 1, page, row, **bf) for _ in range(n_bufs)]
+    like_planes = [torch.randn(B * pages_per, 2, G, page, hd, **bf) for _ in range(2)]
+    table = torch.arange(B * pages_per, **i32).reshape(B, pages_per).contiguous()
+    pos_b, slot_b = torch.full((B,), ctx - 1, **i32), torch.arange(B, **i32)
+    dstep = _PortionStep(pos_b, slot_b, decode=True)
+    qd, ld = q[:B].contiguous(), lat[:B].contiguous()
+    t_new = _graph_time(lambda i: ops.window_attention(qd, None, ld, pages[i % n_bufs], pages[i % n_bufs][..., :rank], table, pos_b,
+                                                       slot_b, H, page, None, row ** -0.5, None, None, fault, dstep, sink=sink))
+    qld, old = ql[:B].contiguous(), ol[:B].contiguous()
+    t_like = _graph_time(lambda i: ops.window_attention(qld, None, old, like_planes[i % 2][:, 0], like_planes[i % 2][:, 1], table,
+                                                        pos_b, slot_b, H, page, None, hd ** -0.5, r1, r2, fault, dstep))
+    put(f"latent attention, {B} decode rows at {ctx}", t_new, B * ctx * row * 2, "GB/s", t_like, B * ctx * 2 * G * hd * 2)
+    del pages, like_planes
+    # ---- between the projections and the cache
+    bufs = 4
+    num_pages = (n + page - 1) // page
+    kp = torch.zeros(num_pages, 1, page, row, **bf)
+    table = torch.arange(num_pages, **i32).reshape(1, num_pages).contiguous()
+    qdim = hd // 2 + rot
+    proj = [torch.randn(n, H * qdim + row, **bf) for _ in range(bufs)]
+    cw = torch.ones(rank, device=dev)
+    cos, sin = torch.ones(n, rot // 2, device=dev), torch.zeros(n, rot // 2, device=dev)
+    t_new = _graph_time(lambda i: ops.latent_prepare(proj[i % bufs], H * qdim, H, hd // 2, rot, rank, cw, 1e-6, cos, sin, q, kp, table,
+                                                     pos, slot, page, fault), 12)
+    plane = torch.zeros(num_pages, 2, G, page, hd, **bf)
+    nq, nk = H * hd, G * hd
+    qkv = [torch.randn(n, nq + 2 * nk, **bf) for _ in range(bufs)]
+    wq, wk = torch.ones(nq, device=dev), torch.ones(nk, device=dev)
+    t_like = _graph_time(lambda i: ops.norm_mix_store(qkv[i % bufs], nq, nk, nk, wq, wk, 1e-6, None, None, plane[:, 0], plane[:, 1],
+                                                      table, pos, slot, page, fault), 12)
+    put(f"rotation, norm, cache write, {n} rows", t_new, n * (2 * H * rot + 2 * row) * 2, "GB/s", t_like, n * (nq + 2 * nk) * 2 * 2)
+    # ---- the recurrences: a prompt portion of one request, and B decode rows
+    nv = H * hd
+    rows = [torch.randn(n, 2 * nk + nv, **bf) for _ in range(2)]
+    beta, a_h, a_c, gt = torch.randn(n, H, **bf), torch.randn(n, H, **bf), torch.randn(n, H * hd, **bf), torch.randn(n, nv, **bf)
+    a_log, dt_h, dt_c, nw = torch.zeros(H, device=dev), torch.zeros(H, device=dev), torch.zeros(H * hd, device=dev), torch.ones(hd, device=dev)
+    st = torch.zeros(max(B, 1), H * hd * hd, device=dev)
+    od = torch.empty(n, nv, **bf)
+    one = (torch.zeros(1, **i32), 1)
+    t_new = _graph_time(lambda i: ops.delta_rule(rows[i % 2], beta, a_h, gt, a_log, dt_h, nw, 1e-6, 1e-6, hd ** -0.5, st, od, slot, last,
+                                                 H, G, hd, hd, requests=1, segments=one, decay_per_head=True, gate_act="silu"), 4)
+    t_like = _graph_time(lambda i: ops.delta_rule(rows[i % 2], beta, a_c, gt, a_log, dt_c, nw, 1e-6, 1e-6, hd ** -0.5, st, od, slot, last,
+                                                  H, G, hd, hd, requests=1, segments=one), 4)
+    put(f"delta rule, decay per head, {n} rows", t_new, 6.0 * n * H * hd * hd, "TFLOP/s", t_like)
+    t_new = _graph_time(lambda i: ops.delta_rule(rows[i % 2][:B], beta[:B], a_h[:B], gt[:B], a_log, dt_h, nw, 1e-6, 1e-6, hd ** -0.5,
+                                                 st, od[:B], slot_b, slot_b, H, G, hd, hd, requests=B, segments=(slot_b, B),
+                                                 decay_per_head=True, gate_act="silu"), 12)
+    t_like_d = _graph_time(lambda i: ops.delta_rule(rows[i % 2][:B], beta[:B], a_c[:B], gt[:B], a_log, dt_c, nw, 1e-6, 1e-6, hd ** -0.5,
+                                                    st, od[:B], slot_b, slot_b, H, G, hd, hd, requests=B, segments=(slot_b, B)), 12)
+    put(f"delta rule, decay per head, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s", t_like_d)
+    lin = [torch.randn(n, 3 * nv, **bf) for _ in range(2)]
+    decay, nwl = torch.full((H,), 0.97, device=dev), torch.ones(nv, device=dev)
+    st.zero_()
+    t_new = _graph_time(lambda i: ops.linear_attention(lin[i % 2], gt, decay, nwl, 1e-6, st, od, slot, last, H, hd, hd, requests=1,
+                                                       segments=one), 4)
+    put(f"linear attention, {n} rows", t_new, 4.0 * n * H * hd * hd, "TFLOP/s", t_like, 6.0 * n * H * hd * hd)
+    t_new = _graph_time(lambda i: ops.linear_attention(lin[i % 2][:B], gt[:B], decay, nwl, 1e-6, st, od[:B], slot_b, slot_b, H, hd, hd,
+                                                       requests=B, segments=(slot_b, B)), 12)
+    put(f"linear attention, {B} decode rows", t_new, B * H * hd * hd * 8, "GB/s", t_like_d)
+    # ---- routed experts: top experts of ffn / (top + 1) hidden elements a row, beside the dense gated unit of top times that
+    Fe = max(32, F // (top + 1) // 32 * 32)
+    w_gu = torch.randn(E, 2, Fe, d, **bf) * 0.02
+    w_dn = torch.randn(E, d, Fe, **bf) * 0.02
+    w_r = torch.randn(E, d, device=dev) * 0.1
+    corr = torch.zeros(E, device=dev)
+    w_sg = torch.randn(d, device=dev) * 0.02
+    dense_gu = torch.randn(d, 2 * top * Fe, **bf) * 0.02
+    dense_dn = torch.randn(top * Fe, d, **bf) * 0.02
+    for label, m in ((f"{B} decode rows", B), (f"{n} rows", n)):
+        xs = [torch.randn(m, d, **bf) for _ in range(bufs)]
+        groups = 4 if E % 4 == 0 and top <= E // 2 else 0
+        t_r = _graph_time(lambda i: ops.moe_route(xs[i % bufs], w_r, corr, w_sg, groups, 2 if groups else 0, top), 12)
+        put(f"router, {label}", t_r, m * d * 2 + E * d * 4, "GB/s")
+        chosen, weights, sgate = ops.moe_route(xs[0], w_r, corr, w_sg, groups, 2 if groups else 0, top)
+        t_new = _graph_time(lambda i: ops.moe_down(ops.moe_gate_up(xs[i % bufs], chosen, w_gu), chosen, weights, w_dn, None, None),
+                            12 if m <= 64 else 3)
+        t_like = _graph_time(lambda i: ops.gemm(ops.gemm_swiglu(xs[i % bufs], dense_gu, top * Fe, 32), dense_dn), 12 if m <= 64 else 3)
+        if m <= 64:
+            used = min(E, m * top)
+            put(f"experts, {label}", t_new, used * 3 * d * Fe * 2, "GB/s", t_like, top * 3 * d * Fe * 2)
+        else:
+            put(f"experts, {label}", t_new, 6.0 * m * top * d * Fe, "TFLOP/s", t_like)
+    return out
+
+
 def sampling(args):
     """The sampling kernel at ``--rows`` rows of ``--vocab`` logits, for the kinds of setting a row can have."""
     dev = "cuda"
@@ -499,7 +637,11 @@ def timeline(args):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
     ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "sampling", "timeline",
-                                     "seqmix", "all"])
+                                     "seqmix", "latent-linear-routed", "all"])
+    ap.add_argument("--rank", type=int, default=128, help="latent-linear-routed: compressed elements a token")
+    ap.add_argument("--rot", type=int, default=64, help="latent-linear-routed: rotated elements a token")
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--top", type=int, default=3)
     ap.add_argument("--window", type=int, default=1024, help="seqmix: keys a row sees")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
@@ -542,6 +684,8 @@ def main(argv=None):
         sampling(args)
     if args.what in ("seqmix", "all"):
         seqmix(args)
+    if args.what in ("latent-linear-routed", "all"):
+        latent_linear_routed(args)
     return 0
 
 
