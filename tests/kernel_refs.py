@@ -301,6 +301,10 @@ def moe_gate_up(x, chosen, w_gate_up):
     return (g * torch.sigmoid(g) * u).reshape(n * top, -1).to(x.dtype)
 
 
+def moe_experts(x, chosen, weights, w_gate_up, w_down, shared, shared_gate):
+    return moe_down(moe_gate_up(x, chosen, w_gate_up), chosen, weights, w_down, shared, shared_gate)
+
+
 def moe_down(hidden, chosen, weights, w_down, shared, shared_gate):
     n, top = chosen.shape
     h = hidden.to(torch.float32).view(n, top, -1)
@@ -554,7 +558,7 @@ def bitmap_set(bitmap_row, tokens):
 _NAMES = ["rotary_fusable", "gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
           "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set", "glu_clamped", "scale_f32", "causal_conv",
           "norm_mix_store", "window_attention", "delta_rule", "linear_attention", "latent_prepare", "gemm_heads", "moe_route",
-          "moe_gate_up", "moe_down"]
+          "moe_gate_up", "moe_down", "moe_experts"]
 
 
 def install(monkeypatch) -> None:

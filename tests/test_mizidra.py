@@ -592,6 +592,43 @@ def test_router_and_experts(dtype, E, top, groups, shared):
     _close(out, ref, 3e-2 if dtype == "bfloat16" else 1e-5, "experts")
 
 
+@gpu
+@pytest.mark.parametrize("n,d,F,E,top", [(300, 64, 96, 6, 3), (40, 96, 32, 16, 3), (1000, 32, 160, 3, 1), (129, 128, 64, 8, 8)])
+def test_experts_of_many_rows(n, d, F, E, top):
+    """Many bfloat16 rows: sorted by expert on the device, tiles on the tensor cores.  Experts that no row chose, experts
+    whose rows end in the middle of a tile, hidden sizes that end in the middle of a tile of columns; beside the kernels
+    that take the same rows one dot product at a time."""
+    from tiny_inference_server_b200.kernels import ops
+    torch.manual_seed(n + E)
+    p = "m."
+    W = {}
+    for e in range(E):
+        W[f"{p}e{e}.gate"], W[f"{p}e{e}.up"] = torch.randn(F, d) / math.sqrt(d), torch.randn(F, d) / math.sqrt(d)
+        W[f"{p}e{e}.down"] = torch.randn(d, F) / math.sqrt(F)
+    W = {k: v.to(torch.bfloat16).double() for k, v in W.items()}
+    x = torch.randn(n, d).to(torch.bfloat16)
+    scores = torch.rand(n, E)
+    if E == 16:
+        scores[:, 5:9] = -1.0                                  # experts 5..8 get no row
+    chosen = scores.topk(top, dim=-1).indices.to(torch.int32)
+    weights = torch.rand(n, top)
+    extra, sgate = torch.randn(n, d).to(torch.bfloat16), torch.rand(n)
+    cdt = lambda t: t.to(torch.bfloat16).cuda().contiguous()
+    w_gu = cdt(torch.stack([torch.stack([W[f"{p}e{e}.gate"], W[f"{p}e{e}.up"]]) for e in range(E)]))
+    w_dn = cdt(torch.stack([W[f"{p}e{e}.down"] for e in range(E)]))
+    before = ops.calls["moe_grouped"]
+    out = ops.moe_experts(x.cuda(), chosen.cuda(), weights.cuda(), w_gu, w_dn, extra.cuda(), sgate.cuda())
+    assert ops.calls["moe_grouped"] == before + 1
+    one_by_one = ops.moe_down(ops.moe_gate_up(x.cuda(), chosen.cuda(), w_gu), chosen.cuda(), weights.cuda(), w_dn, extra.cuda(),
+                              sgate.cuda())
+    ref = sgate.double()[:, None] * extra.double()
+    for e in range(E):
+        share = (weights.double() * (chosen == e)).sum(-1, keepdim=True)
+        ref += share * plain.gated_unit(x.double(), W, f"{p}e{e}.")
+    _close(out, ref, 3e-2, "experts, many rows")
+    _close(one_by_one, ref, 3e-2, "experts, row by row")
+
+
 # ------------------------------------------------------------------------------------------------
 # GPU: the whole model through the engine
 # ------------------------------------------------------------------------------------------------

@@ -18,11 +18,17 @@ typedef cublasStatus_t (*GemmExFn)(cublasHandle_t, cublasOperation_t, cublasOper
                                    const void*, cudaDataType, int, const void*, cudaDataType, int, const void*, void*,
                                    cudaDataType, int, cublasComputeType_t, cublasGemmAlgo_t);
 
+typedef cublasStatus_t (*GemmBatchedFn)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*,
+                                        const void*, cudaDataType, int, long long, const void*, cudaDataType, int, long long,
+                                        const void*, void*, cudaDataType, int, long long, int, cublasComputeType_t,
+                                        cublasGemmAlgo_t);
+
 struct Blas {
     cublasHandle_t handle = nullptr;
     SetStreamFn set_stream = nullptr;
     SetWorkspaceFn set_workspace = nullptr;
     GemmExFn gemm_ex = nullptr;
+    GemmBatchedFn gemm_batched = nullptr;
     bool ok = false;
     int device = -1;                 // the device that was current when the handle was made
     void* workspace = nullptr;       // given once by the caller; set again after every change of stream
@@ -43,6 +49,7 @@ Blas& blas() {
         b.set_stream = reinterpret_cast<SetStreamFn>(dlsym(lib, "cublasSetStream_v2"));
         b.set_workspace = reinterpret_cast<SetWorkspaceFn>(dlsym(lib, "cublasSetWorkspace_v2"));
         b.gemm_ex = reinterpret_cast<GemmExFn>(dlsym(lib, "cublasGemmEx"));
+        b.gemm_batched = reinterpret_cast<GemmBatchedFn>(dlsym(lib, "cublasGemmStridedBatchedEx"));
         if (!create || !b.set_stream || !b.set_workspace || !b.gemm_ex) return;
         if (create(&b.handle) != CUBLAS_STATUS_SUCCESS) return;
         cudaGetDevice(&b.device);
@@ -66,15 +73,8 @@ TIS_API int tis_gemm_library_init(void* workspace, size_t bytes) {
     return 1;
 }
 
-// y = x . W, bfloat16 operands, float32 accumulation; y bfloat16 or (out_f32) float32.  Strides in elements.
-TIS_API int tis_gemm_library(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
-                             int out_f32, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return TIS_OK;
-    Blas& b = blas();
-    if (!b.ok) {
-        tis_set_error("gemm_library: cuBLAS was not found in the process");
-        return TIS_CUDA_ERROR;
-    }
+// The handle on the caller's device and stream, with the caller's workspace.
+static int use_stream(Blas& b, cudaStream_t stream) {
     int dev = -1;
     cudaGetDevice(&dev);
     if (dev != b.device) {
@@ -94,12 +94,51 @@ TIS_API int tis_gemm_library(const void* x, int ldx, const void* w, int ldw, voi
         b.stream = stream;
         b.stream_set = true;
     }
+    return TIS_OK;
+}
+
+// y = x . W, bfloat16 operands, float32 accumulation; y bfloat16 or (out_f32) float32.  Strides in elements.
+TIS_API int tis_gemm_library(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
+                             int out_f32, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return TIS_OK;
+    Blas& b = blas();
+    if (!b.ok) {
+        tis_set_error("gemm_library: cuBLAS was not found in the process");
+        return TIS_CUDA_ERROR;
+    }
+    const int ready = use_stream(b, stream);
+    if (ready != TIS_OK) return ready;
     const float alpha = 1.f, beta = 0.f;
     const cublasStatus_t st = b.gemm_ex(b.handle, CUBLAS_OP_N, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, ldw, x,
                                         CUDA_R_16BF, ldx, &beta, out, out_f32 ? CUDA_R_32F : CUDA_R_16BF, ldo,
                                         CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     if (st != CUBLAS_STATUS_SUCCESS) {
         tis_set_error("gemm_library: cublasGemmEx failed with status %d (M %d N %d K %d)", (int)st, M, N, K);
+        return TIS_CUDA_ERROR;
+    }
+    return TIS_OK;
+}
+
+// y[r][h] = x[r][h] . W[h] for every head h of a batch: x (M, H, K) with row stride ldx and head stride sx, W (H, K, N)
+// contiguous, y (M, H, N) with row stride ldo and head stride so.  dtype bfloat16 (float32 accumulation) or float32
+// (true 32-bit: the default math mode has no reduced-precision path for it).  Strides in elements.
+TIS_API int tis_gemm_library_heads(int dtype, const void* x, int ldx, long long sx, const void* w, void* out, int ldo,
+                                   long long so, int M, int N, int K, int H, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || H <= 0) return TIS_OK;
+    Blas& b = blas();
+    if (!b.ok || !b.gemm_batched) {
+        tis_set_error("gemm_library: cuBLAS (batched products) was not found in the process");
+        return TIS_CUDA_ERROR;
+    }
+    const int ready = use_stream(b, stream);
+    if (ready != TIS_OK) return ready;
+    const float alpha = 1.f, beta = 0.f;
+    const cudaDataType t = dtype == TIS_BF16 ? CUDA_R_16BF : CUDA_R_32F;
+    const cublasStatus_t st = b.gemm_batched(b.handle, CUBLAS_OP_N, CUBLAS_OP_N, N, M, K, &alpha, w, t, N, (long long)K * N, x, t,
+                                             ldx, sx, &beta, out, t, ldo, so, H, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    if (st != CUBLAS_STATUS_SUCCESS) {
+        tis_set_error("gemm_library: cublasGemmStridedBatchedEx failed with status %d (M %d N %d K %d, %d heads)", (int)st, M, N,
+                      K, H);
         return TIS_CUDA_ERROR;
     }
     return TIS_OK;

@@ -882,7 +882,7 @@ delta_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gat
 // out[r, :] = o / sqrt(mean(o^2) + eps) * norm_w * sigmoid(gate) over the whole row (`width` elements, all heads
 // together): a CTA a row.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 row_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gate, int ldg, const float* __restrict__ norm_w,
                     float eps, T* __restrict__ out, int ldo, const int* __restrict__ row_slot, int width) {
     __shared__ float red[33];
@@ -892,9 +892,30 @@ row_out_norm_kernel(const float* __restrict__ o_raw, const T* __restrict__ gate,
     pdl_wait();
     const float* o = o_raw + (size_t)r * width;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(o[j], o[j], ss);
+    const bool vec = width % 4 == 0 && ((uintptr_t)o_raw | (uintptr_t)norm_w) % 16 == 0;
+    if (vec) {
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(o + j);
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(o[j], o[j], ss);
+    }
     ss = block_sum(ss, red);
     const float f = rsqrtf(ss / (float)width + eps);
+    if (vec) {
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(o + j);
+            const float4 w = *reinterpret_cast<const float4*>(norm_w + j);
+            float x[4] = {v.x * f * w.x, v.y * f * w.y, v.z * f * w.z, v.w * f * w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (gate != nullptr) x[e] *= gate_f(to_f32(gate[(size_t)r * ldg + j + e]), 0);
+                out[(size_t)r * ldo + j + e] = from_f32<T>(x[e]);
+            }
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         float x = o[j] * f * norm_w[j];
         if (gate != nullptr) x *= gate_f(to_f32(gate[(size_t)r * ldg + j]), 0);
@@ -913,7 +934,7 @@ static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb,
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK) return st;
     if (decay_mode == DECAY_CONSTANT) {
-        tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
+        tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(256), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
                    row_slot, H * v_dim);
         return tis_check_launch("row_out_norm");
     }
@@ -942,7 +963,7 @@ static int launch_delta_rule(const T* qkv, int ld, const T* b_in, int ldb, const
                k_dim, v_dim, decay_mode, gate_act, decay_mode == DECAY_CONSTANT ? o_raw : (float*)nullptr);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK || decay_mode != DECAY_CONSTANT) return st;
-    tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(128), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
+    tis_launch(row_out_norm_kernel<T>, dim3(n), dim3(256), 0, stream, (const float*)o_raw, gate, ldg, norm_w, eps, out, ldo,
                row_slot, H * v_dim);
     return tis_check_launch("row_out_norm");
 }

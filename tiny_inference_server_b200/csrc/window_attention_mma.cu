@@ -70,7 +70,7 @@ struct Params {
     const float* sink;       // per query head: exp(sink) is one more term of the softmax's denominator (null: none)
     int v_row;               // elements from one value row of a page to the next (VD, or more when the rows are slices)
     int* fault;
-    float* partial;          // [tiles][G][splits][16][VD + 2]: unnormalised out, maximum, sum (key splits over CTAs)
+    float* partial;          // [tiles][G][splits][64][VD + 2]: unnormalised out, maximum, sum (key splits over CTAs)
 };
 
 // Copies the key and value rows first .. first + 63 (those that exist: j <= last) of a request into a stage.  Two
@@ -129,13 +129,11 @@ window_attention_mma_kernel(const Params p) {
     int kt_begin = 0;
     const int splits = gridDim.z;
     if (splits > 1) {
-        // the key tiles of a decode row's tile are shared out over the CTAs of grid.z; any other tile is one CTA's
-        if (!split_keys) { if (blockIdx.z > 0) return; }
-        else {
-            const int per = (ntiles + splits - 1) / splits;
-            kt_begin = min(ntiles, (int)blockIdx.z * per);
-            ntiles = min(ntiles, kt_begin + per);
-        }
+        // the key tiles of a tile of rows are shared out over the CTAs of grid.z (a decode step: few tiles, each with
+        // many keys to walk), whose partial results the merge kernel adds up
+        const int per = (ntiles + splits - 1) / splits;
+        kt_begin = min(ntiles, (int)blockIdx.z * per);
+        ntiles = min(ntiles, kt_begin + per);
     }
     const int base = split_keys ? 0 : warp * 16;               // first packed row of this warp
     // this thread's two packed rows: base + g and base + g + 8
@@ -170,9 +168,10 @@ window_attention_mma_kernel(const Params p) {
 #pragma unroll
     for (int n = 0; n < VD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    if (p.sink != nullptr && !split_keys) {
+    if (p.sink != nullptr && !split_keys && blockIdx.z == 0) {
         // the sink's term: the running maximum starts at the sink and the running sum at 1 (in one of the four
-        // threads that share a row).  Decode rows, whose keys several warps and CTAs share, get it when those merge.
+        // threads that share a row); it counts once, with the first share of the keys.  Rows whose keys the four warps
+        // share get it when those merge.
         if (row_a) { m[0] = p.sink[head_a]; l[0] = t4 == 0 ? 1.f : 0.f; }
         if (row_b) { m[1] = p.sink[head_b]; l[1] = t4 == 0 ? 1.f : 0.f; }
     }
@@ -326,7 +325,7 @@ window_attention_mma_kernel(const Params p) {
                 mm = m2;
             }
             if (splits > 1) {                                  // this CTA's share of the keys: left for the merge kernel
-                float* dst = p.partial + ((((size_t)tile * p.G + kvh) * splits + blockIdx.z) * 16 + mrow) * PS;
+                float* dst = p.partial + ((((size_t)tile * p.G + kvh) * splits + blockIdx.z) * ROWS + mrow) * PS;
                 dst[c] = num;
                 if (c == 0) { dst[VD] = mm; dst[VD + 1] = den; }
                 continue;
@@ -336,6 +335,22 @@ window_attention_mma_kernel(const Params p) {
             const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
             if (p.gate != nullptr) x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + col])));
             p.out[row * p.ldo + col] = __float2bfloat16_rn(x);
+        }
+        return;
+    }
+    if (splits > 1) {                                          // this CTA's share of the keys: left for the merge kernel
+        constexpr int PS = VD + 2;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int mrow = base + g + 8 * h;
+            if (mrow >= packed) continue;
+            float* dst = p.partial + ((((size_t)tile * p.G + kvh) * splits + blockIdx.z) * ROWS + mrow) * PS;
+#pragma unroll
+            for (int n = 0; n < VD / 8; ++n) {
+                dst[n * 8 + 2 * t4] = o[n][2 * h];
+                dst[n * 8 + 2 * t4 + 1] = o[n][2 * h + 1];
+            }
+            if (t4 == 0) { dst[VD] = m[h]; dst[VD + 1] = l[h]; }
         }
         return;
     }
@@ -360,7 +375,8 @@ window_attention_mma_kernel(const Params p) {
     }
 }
 
-// The key splits of decode tiles, merged: a CTA per (tile, kv head), a thread per output element.
+// The key splits of decode tiles, merged: the CTAs of grid.z share the output elements of a (tile, kv head), a thread
+// an element (every thread finds its row's maximum over the splits itself: the few words it reads are in cache).
 __global__ void __launch_bounds__(128)
 window_attention_merge_kernel(const Params p, int splits) {
     pdl_launch_dependents();
@@ -368,17 +384,17 @@ window_attention_merge_kernel(const Params p, int splits) {
     const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
     const int gq = p.H / p.G;
     const int packed = nrows * gq;
-    if (nrows <= 0 || p.row_slot[row0] < 0 || packed > 16) return;      // tiles of many rows were one CTA's
+    if (nrows <= 0 || p.row_slot[row0] < 0) return;
     pdl_wait();
     constexpr int PS = VD + 2;
-    const float* part = p.partial + (((size_t)tile * p.G + kvh) * splits) * 16 * PS;
-    for (int idx = threadIdx.x; idx < packed * VD; idx += blockDim.x) {
+    const float* part = p.partial + (((size_t)tile * p.G + kvh) * splits) * ROWS * PS;
+    for (int idx = blockIdx.z * blockDim.x + threadIdx.x; idx < packed * VD; idx += gridDim.z * blockDim.x) {
         const int mrow = idx / VD, c = idx - mrow * VD;
         float mm = -INFINITY;
-        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part[((size_t)s * 16 + mrow) * PS + VD]);
+        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part[((size_t)s * ROWS + mrow) * PS + VD]);
         float num = 0.f, den = 0.f;
         for (int s = 0; s < splits; ++s) {
-            const float* src = part + ((size_t)s * 16 + mrow) * PS;
+            const float* src = part + ((size_t)s * ROWS + mrow) * PS;
             const float f = src[VD] == -INFINITY ? 0.f : __expf(src[VD] - mm);
             num = fmaf(src[c], f, num);
             den = fmaf(src[VD + 1], f, den);
@@ -395,7 +411,7 @@ window_attention_merge_kernel(const Params p, int splits) {
 
 // Floats of scratch that `splits` key splits of `num_tiles` tiles need.
 TIS_API size_t tis_window_attention_partial_floats(int num_tiles, int G, int splits) {
-    return (size_t)num_tiles * G * splits * 16 * (VD + 2);
+    return (size_t)num_tiles * G * splits * ROWS * (VD + 2);
 }
 
 TIS_API int tis_window_attention_mma_dims(int* kd, int* vd) {
@@ -445,6 +461,8 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
     tis_launch(window_attention_mma_kernel, dim3(num_tiles, G, splits), dim3(THREADS), smem, stream, p);
     int st = tis_check_launch("window_attention_mma");
     if (st != TIS_OK || splits == 1) return st;
-    tis_launch(window_attention_merge_kernel, dim3(num_tiles, G), dim3(128), 0, stream, p, splits);
+    // a step whose keys are split holds one row a tile: H / G packed rows
+    const int rows_bound = H / G < ROWS ? H / G : ROWS;
+    tis_launch(window_attention_merge_kernel, dim3(num_tiles, G, (rows_bound * VD + 127) / 128), dim3(128), 0, stream, p, splits);
     return tis_check_launch("window_attention_merge");
 }

@@ -423,8 +423,7 @@ def latent_linear_routed(args):
         t_r = _graph_time(lambda i: ops.moe_route(xs[i % bufs], w_r, corr, w_sg, groups, 2 if groups else 0, top), 12)
         put(f"router, {label}", t_r, m * d * 2 + E * d * 4, "GB/s")
         chosen, weights, sgate = ops.moe_route(xs[0], w_r, corr, w_sg, groups, 2 if groups else 0, top)
-        t_new = _graph_time(lambda i: ops.moe_down(ops.moe_gate_up(xs[i % bufs], chosen, w_gu), chosen, weights, w_dn, None, None),
-                            12 if m <= 64 else 3)
+        t_new = _graph_time(lambda i: ops.moe_experts(xs[i % bufs], chosen, weights, w_gu, w_dn, None, None), 12 if m <= 64 else 3)
         t_like = _graph_time(lambda i: ops.gemm(ops.gemm_swiglu(xs[i % bufs], dense_gu, top * Fe, 32), dense_dn), 12 if m <= 64 else 3)
         if m <= 64:
             used = min(E, m * top)

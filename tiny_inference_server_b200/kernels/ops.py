@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 6
+ABI_VERSION = 7
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -404,6 +404,17 @@ LIBRARY_GEMM_DIRECT = os.environ.get("TIS_LIBRARY_GEMM", "direct") != "torch"
 _blas_state = None          # None: not tried yet; False: unavailable; else the workspace tensor
 
 
+def _blas_workspace(lib, device) -> bool:
+    """Give the library its workspace at the first call; False when cuBLAS cannot be called directly."""
+    global _blas_state
+    if not LIBRARY_GEMM_DIRECT or _blas_state is False:
+        return False
+    if _blas_state is None:
+        ws = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+        _blas_state = ws if lib.tis_gemm_library_init(_p(ws), ctypes.c_size_t(ws.numel())) else False
+    return _blas_state is not False
+
+
 def _library_gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], f32_out: bool) -> Optional[torch.Tensor]:
     """``a @ w`` by a direct cuBLAS call, or None when that is not possible (then torch.mm does it)."""
     global _blas_state, launches
@@ -413,11 +424,8 @@ def _library_gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
             or a.stride(0) < a.shape[1] or w.stride(0) < w.shape[1]):
         return None
     lib = library()
-    if _blas_state is None:
-        ws = torch.empty(32 << 20, dtype=torch.uint8, device=a.device)
-        _blas_state = ws if lib.tis_gemm_library_init(_p(ws), ctypes.c_size_t(ws.numel())) else False
-        if _blas_state is False:
-            return None
+    if not _blas_workspace(lib, a.device):
+        return None
     n, k = a.shape
     cols = w.shape[1]
     want = torch.float32 if f32_out else torch.bfloat16
@@ -1015,6 +1023,15 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
     if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
     calls["gemm_heads"] += 1
+    n, heads, k = a.shape
+    cols = w.shape[2]
+    lib = library()
+    if _blas_workspace(lib, a.device) and a.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous() and a.dtype == w.dtype == out.dtype:
+        status = lib.tis_gemm_library_heads(_dt(a), _p(a), a.stride(0), ctypes.c_longlong(a.stride(1)), _p(w), _p(out),
+                                            out.stride(0), ctypes.c_longlong(out.stride(1)), n, cols, k, heads, _stream())
+        if status != 0:
+            raise KernelError(lib.tis_last_error().decode())
+        return out
     out.copy_(torch.bmm(a.transpose(0, 1), w).transpose(0, 1))
     return out
 
@@ -1109,3 +1126,39 @@ def sample_stage_limit(entries: int) -> None:
 def bitmap_set(bitmap_row: torch.Tensor, tokens: torch.Tensor) -> None:
     lib = library()
     _check(lib.tis_bitmap_set(_p(bitmap_row), _p(tokens), tokens.numel(), _stream()), lib)
+
+
+#: (token, choice) pairs from which bfloat16 expert products go to the tiles on the tensor cores (rows sorted by expert on
+#: the device) instead of one dot product per output element; TIS_MOE_GROUPED_MIN_PAIRS overrides (0: never)
+MOE_GROUPED_MIN_PAIRS = int(os.environ.get("TIS_MOE_GROUPED_MIN_PAIRS", "96"))
+
+
+def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                shared: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor]) -> torch.Tensor:
+    """``out[r] = sum_k weights[r, k] * unit(chosen[r, k])(x[r]) (+ shared_gate[r] * shared[r])`` with the gated units
+    ``unit(e)(x) = Wd[e] (silu(Wg[e] x) * (Wu[e] x))``: ``w_gate_up`` (E, 2, F, d), ``w_down`` (E, d, F).  Few rows, and
+    float32: ``moe_gate_up`` and ``moe_down`` (a dot product per output element, the weights read where they lie).  Many
+    bfloat16 rows: the rows are sorted by expert on the device and every expert's rows run as tiles on the tensor
+    cores; nothing is read back, so either way the step can be captured in a graph."""
+    n, d = x.shape
+    top = chosen.shape[1]
+    experts, _, hidden, _ = w_gate_up.shape
+    if (x.dtype == torch.bfloat16 and MOE_GROUPED_MIN_PAIRS > 0 and n * top >= MOE_GROUPED_MIN_PAIRS and d % 32 == 0
+            and hidden % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and (shared is None or (shared.stride(1) == 1 and shared.stride(0) % 2 == 0))):
+        lib = library()
+        tiles = lib.tis_moe_grouped_tiles(n * top, experts)
+        dev = x.device
+        meta = torch.empty(tiles * 64 + n * top + tiles, dtype=torch.int32, device=dev)
+        sorted_pair, pair_place, tile_expert = meta[:tiles * 64], meta[tiles * 64:tiles * 64 + n * top], meta[tiles * 64 + n * top:]
+        hid = torch.empty((tiles * 64, hidden), dtype=x.dtype, device=dev)
+        y = torch.empty((tiles * 64, d), dtype=x.dtype, device=dev)
+        out = torch.empty((n, d), dtype=x.dtype, device=dev)
+        calls["moe_grouped"] += 1
+        global launches
+        launches += 3
+        _check(lib.tis_moe_grouped(_p(x), x.stride(0), _p(chosen), _p(weights), _p(w_gate_up), _p(w_down), _p(shared),
+                                   shared.stride(0) if shared is not None else 0, _p(shared_gate), _p(out), _p(sorted_pair),
+                                   _p(pair_place), _p(tile_expert), _p(hid), _p(y), n, d, top, experts, hidden, _stream()), lib)
+        return out
+    return moe_down(moe_gate_up(x, chosen, w_gate_up), chosen, weights, w_down, shared, shared_gate)

@@ -179,9 +179,8 @@ class RoutedExperts(FeedForward):
     def forward(self, x, step=None):
         chosen, weights, shared_gate = ops.moe_route(x, self.w_router, self.correction, self.w_shared_gate, self.groups,
                                                      self.keep, self.top, self.WEIGHT_EPS)
-        hidden = ops.moe_gate_up(x, chosen, self.w_gate_up)
         shared = self.shared.forward(x, step) if self.shared is not None else None
-        return ops.moe_down(hidden, chosen, weights, self.w_down, shared, shared_gate)
+        return ops.moe_experts(x, chosen, weights, self.w_gate_up, self.w_down, shared, shared_gate)
 
 
 register_part("ffn", "swiglu", SwiGLU)
