@@ -244,12 +244,12 @@ def linear_attention(qkv, gate, decay, norm_weight, eps, state, out, row_slot, r
 
 def latent_prepare(proj, dkv_at, num_heads, flat_dim, rot_dim, rank, c_weight, eps, cos, sin, q_out, k_pages, block_table,
                    positions, row_slot, page_size, fault):
-    half = rot_dim // 2
+    half = cos.shape[1]
     qd, row_w = flat_dim + rot_dim, rank + rot_dim
 
     def turn(x, c, s):
-        a, b = x[..., :half], x[..., half:]
-        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+        a, b = x[..., :half], x[..., half:2 * half]
+        return torch.cat([a * c - b * s, b * c + a * s, x[..., 2 * half:]], dim=-1)
 
     for r in range(proj.shape[0]):
         slot = int(row_slot[r])

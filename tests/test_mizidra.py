@@ -31,8 +31,8 @@ def _delta(heads, kv, dim, vdim, conv):
     return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv}
 
 
-def _latent(heads, dim, rot, vdim, rank, base=10000.0, scaling=None, scale=None):
-    r = {"base": base, "dims": rot}
+def _latent(heads, dim, rot, vdim, rank, base=10000.0, scaling=None, scale=None, dims=None):
+    r = {"base": base, "dims": dims or rot}
     if scaling:
         r["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
     return {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "rot": r,
@@ -68,7 +68,7 @@ M2 = dict(architecture="Mizidra", vocab=67, width=32, norm={"eps": 1e-6}, layers
 ])
 # sizes that fit no vector, tile or alignment: every kernel's plain path
 M3 = dict(architecture="Mizidra", vocab=53, width=40, norm={"eps": 1e-6}, layers=[
-    {"type": "latent_attention", "mixer": _latent(3, 10, 6, 7, 22, base=100.0), "mlp": _moe(5, 2, 27, shared=13)},
+    {"type": "latent_attention", "mixer": _latent(3, 10, 6, 7, 22, base=100.0, dims=4), "mlp": _moe(5, 2, 27, shared=13)},
     {"type": "lightning", "mixer": _lightning(3, 10, 6, (0.5, 0.8, 0.97)), "mlp": _moe(5, 2, 27)},
     {"type": "delta", "mixer": _delta(2, 1, 6, 10, 6), "mlp": None},
 ])
@@ -231,7 +231,7 @@ def test_config_errors_name_the_problem():
     with pytest.raises(ConfigError, match="exceeds"):
         config_from_dict(broken(lambda c: c["layers"][0]["mlp"]["router"].update(top=5)))
     with pytest.raises(ConfigError, match="rot.dims"):
-        config_from_dict(broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=6)))
+        config_from_dict(broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=10)))
     with pytest.raises(ConfigError, match="missing keys: width"):
         config_from_dict(broken(lambda c: c.pop("width")))
 
@@ -451,9 +451,9 @@ class _Step:
 
 @gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,flat,rot,rank,page", [(4, 16, 8, 40, 16), (2, 8, 16, 16, 4), (3, 10, 6, 22, 12), (8, 32, 16, 48, 16),
-                                                  (1, 16, 16, 16, 8), (16, 8, 32, 96, 16)])
-def test_latent_cache_sink_and_a_key_far_back(dtype, H, flat, rot, rank, page):
+@pytest.mark.parametrize("H,flat,rot,rank,page,dims", [(4, 16, 8, 40, 16, 8), (2, 8, 16, 16, 4, 12), (3, 10, 6, 22, 12, 2),
+                                                       (8, 32, 16, 48, 16, 16), (1, 16, 16, 16, 8, 16), (16, 8, 32, 96, 16, 32)])
+def test_latent_cache_sink_and_a_key_far_back(dtype, H, flat, rot, rank, page, dims):
     """The step between the projections and the cache (norm of the compressed vector, rotation of the shared key
     slice and of the queries' slices) and attention with a sink over that cache, in portions and single rows over
     scattered pages.  Rows near the end ask for key 3, several hundred keys back, and for the keys at the last and
@@ -463,7 +463,7 @@ def test_latent_cache_sink_and_a_key_far_back(dtype, H, flat, rot, rank, page):
     torch.manual_seed(H * 10 + rank)
     L = 333
     qd, row = flat + rot, rank + rot
-    rot_cfg = {"dims": rot, "base": 1000.0, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}
+    rot_cfg = {"dims": dims, "base": 1000.0, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}
     proj = torch.randn(L, H * qd + row + 3)                # three columns of padding behind
     dkv_at = H * qd
     sink = torch.randn(H)
@@ -501,7 +501,7 @@ def test_latent_cache_sink_and_a_key_far_back(dtype, H, flat, rot, rank, page):
     table[1, :len(perm)] = perm
     table = table.cuda()
     fault = torch.zeros(4, dtype=torch.int32, device="cuda")
-    cos, sin = (t.cuda() for t in RotaryRescaled(rot, 1000.0, 512, scaling=rot_cfg["scaling"]).tables())
+    cos, sin = (t.cuda() for t in RotaryRescaled(rot, 1000.0, 512, scaling=rot_cfg["scaling"], rotary_dim=dims).tables())
     got = torch.zeros(L, H * rank, dtype=DT[dtype], device="cuda")
     fed, i = 0, 0
     cuts = [5, 2, 1, 1, 30, 2, 64, 100]

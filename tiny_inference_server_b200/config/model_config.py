@@ -416,8 +416,9 @@ class MizidraConfig:
                 rot = m.get("rot")
                 if not isinstance(rot, dict) or not isinstance(rot.get("base"), (int, float)) or rot["base"] <= 0:
                     errs.append(f"layers[{i}].mixer.rot.base is missing")
-                elif rot.get("dims", m["rot_dim"]) != m["rot_dim"] or m["rot_dim"] % 2:
-                    errs.append(f"layers[{i}].mixer: rot.dims must equal rot_dim ({m['rot_dim']}) and be even")
+                elif not _positive_int(rot.get("dims", m["rot_dim"])) or rot.get("dims", m["rot_dim"]) > m["rot_dim"] \
+                        or rot.get("dims", m["rot_dim"]) % 2:
+                    errs.append(f"layers[{i}].mixer: rot.dims must be even and at most rot_dim ({m['rot_dim']})")
                 elif rot.get("scaling"):
                     sc = rot["scaling"]
                     miss = [k for k in ("factor", "original", "fast", "slow") if not isinstance(sc.get(k), (int, float))]

@@ -5,13 +5,14 @@
 
 // A row of `proj` holds, per head, flat + rot query elements, and from column dkv_at on rank + rot elements of the
 // compressed projection.  Per row (a CTA):
-//   * the last rot elements of every head's query are rotated by the row's position (pairs (i, i + rot / 2), angles from
-//     the tables cos / sin [positions][rot / 2]) and written to q_out[row][head * (rank + rot) + rank ...];
+//   * the last rot elements of every head's query are rotated by the row's position (the first `dims` of them, in pairs
+//     (i, i + dims / 2) with angles from the tables cos / sin [positions][dims / 2]; the rest pass unchanged) and written to
+//     q_out[row][head * (rank + rot) + rank ...];
 //   * c = x[0 .. rank) * rsqrt(mean(x^2) + eps) * cw and the rotated last rot elements of the compressed projection are
 //     written as the row [c | slice] of the position's page: k_pages + page * page_stride + in_page * (rank + rot).
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ proj, int ld, int dkv_at, int H, int flat, int rot, int rank,
+latent_prepare_kernel(const T* __restrict__ proj, int ld, int dkv_at, int H, int flat, int rot, int dims, int rank,
                       const float* __restrict__ cw, float eps, const float* __restrict__ cos_t,
                       const float* __restrict__ sin_t, int table_rows, T* __restrict__ q_out, int ldq,
                       T* __restrict__ k_pages, size_t page_stride, int page_size, int num_pages,
@@ -24,7 +25,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int dkv_at, int H, int
     if (slot < 0) return;
     const int pos = positions[r];
     const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
-    const int half = rot / 2, tid = threadIdx.x, nthr = blockDim.x;
+    const int half = dims / 2, rest = rot - dims, tid = threadIdx.x, nthr = blockDim.x;
     if (pos < 0 || pos >= table_rows || page < 0 || page >= num_pages) {
         if (tid == 0) atomicExch(fault, 6);
         return;
@@ -42,6 +43,10 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int dkv_at, int H, int
         dst[i] = from_f32<T>(a * c - b * s);
         dst[half + i] = from_f32<T>(b * c + a * s);
     }
+    for (int idx = tid; idx < H * rest; idx += nthr) {       // the channels of the slice that are not rotated
+        const int h = idx / rest, i = dims + idx - h * rest;
+        q_out[(size_t)r * ldq + (size_t)h * rw + rank + i] = row[h * qd + flat + i];
+    }
     const T* low = row + dkv_at;
     float ss = 0.f;
     for (int i = tid; i < rank; i += nthr) { const float v = to_f32(low[i]); ss = fmaf(v, v, ss); }
@@ -55,22 +60,24 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int dkv_at, int H, int
         dst[rank + i] = from_f32<T>(a * c - b * s);
         dst[rank + half + i] = from_f32<T>(b * c + a * s);
     }
+    for (int i = dims + tid; i < rot; i += nthr) dst[rank + i] = low[rank + i];
 }
 
-TIS_API int tis_latent_prepare(int dtype, const void* proj, int ld, int dkv_at, int H, int flat, int rot, int rank,
+TIS_API int tis_latent_prepare(int dtype, const void* proj, int ld, int dkv_at, int H, int flat, int rot, int dims, int rank,
                                const float* cw, float eps, const float* cos_t, const float* sin_t, int table_rows,
                                void* q_out, int ldq, void* k_pages, size_t page_stride, int page_size, int num_pages,
                                const int* block_table, int bt_stride, const int* positions, const int* row_slot,
                                int* fault, int n, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
-    if (H <= 0 || flat < 0 || rot <= 0 || rot % 2 || rank <= 0 || page_size <= 0 || dkv_at < H * (flat + rot)) {
-        tis_set_error("latent_prepare: %d heads, %d + %d query elements a head, rank %d, page size %d", H, flat, rot, rank,
-                      page_size);
+    if (H <= 0 || flat < 0 || rot <= 0 || dims <= 0 || dims % 2 || dims > rot || rank <= 0 || page_size <= 0 ||
+        dkv_at < H * (flat + rot)) {
+        tis_set_error("latent_prepare: %d heads, %d + %d query elements a head of which %d rotated, rank %d, page size %d", H,
+                      flat, rot, dims, rank, page_size);
         return TIS_BAD_SIZE;
     }
     TIS_DISPATCH_DTYPE(dtype, T,
-        tis_launch(latent_prepare_kernel<T>, dim3(n), dim3(128), 0, stream, (const T*)proj, ld, dkv_at, H, flat, rot, rank,
-                   cw, eps, cos_t, sin_t, table_rows, (T*)q_out, ldq, (T*)k_pages, page_stride, page_size, num_pages,
+        tis_launch(latent_prepare_kernel<T>, dim3(n), dim3(128), 0, stream, (const T*)proj, ld, dkv_at, H, flat, rot, dims,
+                   rank, cw, eps, cos_t, sin_t, table_rows, (T*)q_out, ldq, (T*)k_pages, page_stride, page_size, num_pages,
                    block_table, bt_stride, positions, row_slot, fault));
     return tis_check_launch("latent_prepare");
 }

@@ -40,6 +40,7 @@ __device__ __forceinline__ void warp_dots(const T* const (&w)[ND], const float* 
 #pragma unroll
     for (int j = 0; j < ND; ++j) acc[j] = 0.f;
     if (vec) {
+#pragma unroll(ND * N >= 32 ? 2 : 4)
         for (int i = lane * N; i < d; i += 32 * N) {
             float v[ND][N];
 #pragma unroll

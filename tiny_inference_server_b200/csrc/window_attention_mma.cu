@@ -375,32 +375,37 @@ window_attention_mma_kernel(const Params p) {
     }
 }
 
-// The key splits of decode tiles, merged: the CTAs of grid.z share the output elements of a (tile, kv head), a thread
-// an element (every thread finds its row's maximum over the splits itself: the few words it reads are in cache).
+// The key splits of a tile, merged: a CTA per (tile, kv head, packed row).  The splits' maxima and sums of the row
+// are read once, by a thread each, and turned into one factor per split in shared memory; then a thread per output
+// column adds up the splits' partial outputs with those factors.
 __global__ void __launch_bounds__(128)
 window_attention_merge_kernel(const Params p, int splits) {
+    __shared__ float factor[64];
+    __shared__ float red[33];
     pdl_launch_dependents();
-    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int tile = blockIdx.x, kvh = blockIdx.y, mrow = blockIdx.z;
     const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
     const int gq = p.H / p.G;
     const int packed = nrows * gq;
-    if (nrows <= 0 || p.row_slot[row0] < 0) return;
+    if (nrows <= 0 || p.row_slot[row0] < 0 || mrow >= packed) return;
     pdl_wait();
     constexpr int PS = VD + 2;
-    const float* part = p.partial + (((size_t)tile * p.G + kvh) * splits) * ROWS * PS;
-    for (int idx = blockIdx.z * blockDim.x + threadIdx.x; idx < packed * VD; idx += gridDim.z * blockDim.x) {
-        const int mrow = idx / VD, c = idx - mrow * VD;
-        float mm = -INFINITY;
-        for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part[((size_t)s * ROWS + mrow) * PS + VD]);
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float* src = part + ((size_t)s * ROWS + mrow) * PS;
-            const float f = src[VD] == -INFINITY ? 0.f : __expf(src[VD] - mm);
-            num = fmaf(src[c], f, num);
-            den = fmaf(src[VD + 1], f, den);
-        }
-        float x = den > 0.f ? num / den : 0.f;
-        const size_t row = (size_t)(row0 + mrow / gq);
+    const float* part = p.partial + ((((size_t)tile * p.G + kvh) * splits) * ROWS + mrow) * PS;
+    const size_t step = (size_t)ROWS * PS;               // from one split's row to the next split's
+    const int tid = threadIdx.x;
+    float m_s = -INFINITY, l_s = 0.f;
+    if (tid < splits) { m_s = part[tid * step + VD]; l_s = part[tid * step + VD + 1]; }
+    const float mm = block_max(m_s, red);
+    const float f = (tid < splits && m_s != -INFINITY) ? __expf(m_s - mm) : 0.f;
+    if (tid < 64) factor[tid] = f;
+    const float den = block_sum(l_s * f, red);            // its barriers also publish the factors
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const size_t row = (size_t)(row0 + mrow / gq);
+    for (int c = tid; c < VD; c += blockDim.x) {
+        float num = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) num = fmaf(part[s * step + c], factor[s], num);
+        float x = num * inv;
         const size_t col = (size_t)(kvh * gq + mrow % gq) * VD + c;
         if (p.gate != nullptr) x = x / (1.f + __expf(-__bfloat162float(p.gate[row * p.ldg + col])));
         p.out[row * p.ldo + col] = __float2bfloat16_rn(x);
@@ -463,6 +468,6 @@ TIS_API int tis_window_attention_mma(const void* q, int ldq, const void* gate, i
     if (st != TIS_OK || splits == 1) return st;
     // a step whose keys are split holds one row a tile: H / G packed rows
     const int rows_bound = H / G < ROWS ? H / G : ROWS;
-    tis_launch(window_attention_merge_kernel, dim3(num_tiles, G, (rows_bound * VD + 127) / 128), dim3(128), 0, stream, p, splits);
+    tis_launch(window_attention_merge_kernel, dim3(num_tiles, G, rows_bound), dim3(128), 0, stream, p, splits);
     return tis_check_launch("window_attention_merge");
 }

@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 7
+ABI_VERSION = 8
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -1001,18 +1001,18 @@ def latent_prepare(proj: torch.Tensor, dkv_at: int, num_heads: int, flat_dim: in
     """Between the projections and the cache of attention over compressed keys and values.  A row of ``proj`` holds,
     per head, ``flat_dim + rot_dim`` query elements, and from column ``dkv_at`` on ``rank + rot_dim`` elements of the
     compressed projection.  The first ``rank`` of those, divided by their root mean square (eps inside the root) and
-    multiplied by ``c_weight``, and the last ``rot_dim``, rotated by the row's position (pairs (i, i + rot_dim / 2),
-    tables ``cos, sin`` [positions, rot_dim / 2] float32), are written as the row ``[c | rotated slice]`` of the
+    multiplied by ``c_weight``, and the last ``rot_dim``, rotated by the row's position (the first ``dims`` of them, in
+    pairs (i, i + dims / 2), with tables ``cos, sin`` [positions, dims / 2] float32; the rest pass unchanged), are written as the row ``[c | rotated slice]`` of the
     position's page in ``k_pages`` [pages, 1, page_size, rank + rot_dim].  The last ``rot_dim`` elements of every
     head's query, rotated the same way, go to ``q_out`` (n, H * (rank + rot_dim)) behind the ``rank`` places that
     the caller fills.  Everything is computed in 32-bit."""
     lib = library()
     n = proj.shape[0]
-    if k_pages.shape[1] != 1 or k_pages.shape[3] != rank + rot_dim or cos.shape[1] * 2 != rot_dim:
+    if k_pages.shape[1] != 1 or k_pages.shape[3] != rank + rot_dim or cos.shape[1] * 2 > rot_dim:
         raise KernelError("latent_prepare: the cache rows or the rotation tables do not fit the sizes")
     kps, _ = _page_strides(k_pages, rank + rot_dim)
-    _check(lib.tis_latent_prepare(_dt(proj), _p(proj), proj.stride(0), dkv_at, num_heads, flat_dim, rot_dim, rank,
-                                  _p(c_weight), _f(eps), _p(cos), _p(sin), cos.shape[0], _p(q_out), q_out.stride(0),
+    _check(lib.tis_latent_prepare(_dt(proj), _p(proj), proj.stride(0), dkv_at, num_heads, flat_dim, rot_dim,
+                                  2 * cos.shape[1], rank, _p(c_weight), _f(eps), _p(cos), _p(sin), cos.shape[0], _p(q_out), q_out.stride(0),
                                   _p(k_pages), kps, page_size, k_pages.shape[0], _p(block_table), block_table.stride(0),
                                   _p(positions), _p(row_slot), _p(fault), n, _stream()), lib)
 

@@ -20,8 +20,8 @@ class LatentAttention(Mixer):
     * ``Wdkv h``: the first ``rank`` elements, divided by their root mean square (``eps`` inside the root) and
       multiplied by ``dkv.norm``, are ``c``; the last ``rot_dim``, rotated, are the shared key slice;
     * head h: key ``Wuk[h] c``, value ``Wuv[h] c``; score ``(q_flat . Wuk[h] c + q_rot . k_rot) * scale``;
-      the rotation (``position``, a ``RotaryHalf`` family member over ``rot_dim`` channels) is applied to
-      ``q_rot`` and the key slice only;
+      the rotation (``position``, a ``RotaryHalf`` family member over the first ``position.rotary_dim`` of the
+      ``rot_dim`` channels) is applied to ``q_rot`` and the key slice only;
     * softmax over the keys ``0..p`` with, when ``has_sink``, one more term ``exp(sink[h])`` in the denominator that
       has no key and no value;
     * ``Wo`` on the heads' outputs side by side.
@@ -53,7 +53,8 @@ class LatentAttention(Mixer):
     def from_config(cls, cfg, prefix: str, layer_index: int, lag: int = 0, position=None):
         m = cfg.layers[layer_index]["mixer"]
         rot = m["rot"]
-        pos = RotaryRescaled(m["rot_dim"], rot["base"], cfg.max_context, scaling=rot.get("scaling"))
+        pos = RotaryRescaled(m["rot_dim"], rot["base"], cfg.max_context, scaling=rot.get("scaling"),
+                             rotary_dim=rot.get("dims", m["rot_dim"]))
         return cls(cfg.hidden_size, m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["scale"],
                    cfg.rms_norm_eps, pos, prefix=prefix)
 
