@@ -8,24 +8,6 @@ namespace {
 
 constexpr int MOE_THREADS = 128;
 
-// sum_i w[i] * xs[i] over a warp: 16-byte loads of the weights when `vec` (d a multiple of a vector, w aligned).
-template <typename T>
-__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* __restrict__ xs, int d, int lane, bool vec) {
-    constexpr int N = Vec16<T>::N;
-    float acc = 0.f;
-    if (vec) {
-        float v[N];
-        for (int i = lane * N; i < d; i += 32 * N) {
-            Vec16<T>::load(w + i, v);
-#pragma unroll
-            for (int e = 0; e < N; ++e) acc = fmaf(v[e], xs[i + e], acc);
-        }
-    } else {
-        for (int i = lane; i < d; i += 32) acc = fmaf(to_f32(w[i]), xs[i], acc);
-    }
-    return warp_sum(acc);
-}
-
 // ND dot products at once, out[j] = sum_i w[j][i] * x[j][i] over a warp: the loads of all of them are in flight together,
 // which is what a kernel that streams weights once lives on.
 //
@@ -432,11 +414,16 @@ moe_grouped_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ 
         }
         asm volatile("cp.async.commit_group;\n" ::);
     };
-    float acc[GATED ? 2 : 1][GT_COLS / 8][4];
+    // the four warps as 2 x 2: a warp owns 32 rows x 32 columns (of the gate and of the up matrix), so that an operand
+    // fragment it loads serves two products
+    const int wm = warp >> 1, wn = warp & 1;
+    float acc[GATED ? 2 : 1][2][4][4];
 #pragma unroll
     for (int h = 0; h < (GATED ? 2 : 1); ++h)
 #pragma unroll
-        for (int n = 0; n < GT_COLS / 8; ++n) { acc[h][n][0] = acc[h][n][1] = acc[h][n][2] = acc[h][n][3] = 0.f; }
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+            for (int n = 0; n < 4; ++n) { acc[h][mi][n][0] = acc[h][mi][n][1] = acc[h][mi][n][2] = acc[h][mi][n][3] = 0.f; }
     const int nk = K / GT_BK;
 #pragma unroll
     for (int s = 0; s < GT_STAGES - 1; ++s) {
@@ -452,16 +439,21 @@ moe_grouped_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ 
         const int s = kt % GT_STAGES;
 #pragma unroll
         for (int kk = 0; kk < GT_BK / 16; ++kk) {
-            unsigned a[4];
-            g_ldmatrix_x4(a, &As[s][warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][kk * 16 + 8 * (lane >> 4)]);
+            unsigned a[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+                g_ldmatrix_x4(a[mi], &As[s][wm * 32 + mi * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][kk * 16 + 8 * (lane >> 4)]);
 #pragma unroll
             for (int h = 0; h < (GATED ? 2 : 1); ++h) {
 #pragma unroll
-                for (int n2 = 0; n2 < GT_COLS / 16; ++n2) {
+                for (int n2 = 0; n2 < 2; ++n2) {
                     unsigned b[4];
-                    g_ldmatrix_x4(b, &Bs[s][h * GT_COLS + n2 * 16 + (lane & 7) + 8 * (lane >> 4)][kk * 16 + 8 * ((lane >> 3) & 1)]);
-                    g_mma_bf16(acc[h][2 * n2], a, b[0], b[1]);
-                    g_mma_bf16(acc[h][2 * n2 + 1], a, b[2], b[3]);
+                    g_ldmatrix_x4(b, &Bs[s][h * GT_COLS + wn * 32 + n2 * 16 + (lane & 7) + 8 * (lane >> 4)][kk * 16 + 8 * ((lane >> 3) & 1)]);
+#pragma unroll
+                    for (int mi = 0; mi < 2; ++mi) {
+                        g_mma_bf16(acc[h][mi][2 * n2], a[mi], b[0], b[1]);
+                        g_mma_bf16(acc[h][mi][2 * n2 + 1], a[mi], b[2], b[3]);
+                    }
                 }
             }
         }
@@ -469,18 +461,21 @@ moe_grouped_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ 
     asm volatile("cp.async.wait_group 0;\n" ::);
     const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const size_t row = (size_t)tile * GT_ROWS + warp * 16 + g + 8 * half;
+    for (int mi = 0; mi < 2; ++mi) {
 #pragma unroll
-        for (int n = 0; n < GT_COLS / 8; ++n) {
-            const int col = n0 + n * 8 + 2 * t4;
-            float v0 = acc[0][n][2 * half], v1 = acc[0][n][2 * half + 1];
-            if (GATED) {
-                v0 = v0 / (1.f + __expf(-v0)) * acc[GATED ? 1 : 0][n][2 * half];
-                v1 = v1 / (1.f + __expf(-v1)) * acc[GATED ? 1 : 0][n][2 * half + 1];
+        for (int half = 0; half < 2; ++half) {
+            const size_t row = (size_t)tile * GT_ROWS + wm * 32 + mi * 16 + g + 8 * half;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const int col = n0 + wn * 32 + n * 8 + 2 * t4;
+                float v0 = acc[0][mi][n][2 * half], v1 = acc[0][mi][n][2 * half + 1];
+                if (GATED) {
+                    v0 = v0 / (1.f + __expf(-v0)) * acc[GATED ? 1 : 0][mi][n][2 * half];
+                    v1 = v1 / (1.f + __expf(-v1)) * acc[GATED ? 1 : 0][mi][n][2 * half + 1];
+                }
+                if (col + 1 < N) *reinterpret_cast<__nv_bfloat162*>(C + row * ldc + col) = __floats2bfloat162_rn(v0, v1);
+                else if (col < N) C[row * ldc + col] = __float2bfloat16_rn(v0);
             }
-            if (col + 1 < N) *reinterpret_cast<__nv_bfloat162*>(C + row * ldc + col) = __floats2bfloat162_rn(v0, v1);
-            else if (col < N) C[row * ldc + col] = __float2bfloat16_rn(v0);
         }
     }
 }
