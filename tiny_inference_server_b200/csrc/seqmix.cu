@@ -708,7 +708,7 @@ delta_rule_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in,
 // a column read different banks with 16-byte loads.  A chunk is prepared by all threads, NT / 16 to a token; the raw
 // values of the next chunk are loaded into registers before the current chunk is walked.  The outputs leave
 // unnormalised, in 32-bit (`o_raw`, (n, H * v_dim)); delta_out_norm_kernel normalises them.
-template <typename T, int DL, int LANES, int COLS>
+template <typename T, int DL, int LANES, int COLS, bool PLAIN>
 __global__ void __launch_bounds__(COLS * LANES)
 delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ b_in, int ldb, const T* __restrict__ a_in,
                         int lda, const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
@@ -736,7 +736,9 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
     const int kvh = head / (H / G);
     const int tid = threadIdx.x;
     const int col = tid / LANES, part = tid % LANES;
-    const bool plain = decay_mode == DECAY_CONSTANT;
+    // PLAIN: the decay is a constant per head and the state takes k v^T as it is, so the walk needs neither the decays of
+    // the chunk nor the first of its two sums over the lanes of a column
+    constexpr bool plain = PLAIN;
     const float decay_rate = plain ? A_log[head] : expf(A_log[head]);
     float* S_glob = state + (size_t)slot * state_stride + (size_t)head * KDIM * v_dim + col0 + col;
     float S[DL];
@@ -829,16 +831,21 @@ delta_rule_split_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__
                 vc = vs[t][col];
                 bc = betas[t];
             }
-            float d0 = 0.f, d1 = 0.f;
+            float d0 = 0.f, d1 = 0.f, u = vc;
+            if (plain) {
 #pragma unroll
-            for (int i = 0; i < DL / 2; ++i) {
-                S[2 * i] *= gc[i].x; S[2 * i + 1] *= gc[i].y;
-                d0 = fmaf(S[2 * i], kc[i].x, d0); d1 = fmaf(S[2 * i + 1], kc[i].y, d1);
+                for (int i = 0; i < DL; ++i) S[i] *= decay_rate;
+            } else {
+#pragma unroll
+                for (int i = 0; i < DL / 2; ++i) {
+                    S[2 * i] *= gc[i].x; S[2 * i + 1] *= gc[i].y;
+                    d0 = fmaf(S[2 * i], kc[i].x, d0); d1 = fmaf(S[2 * i + 1], kc[i].y, d1);
+                }
+                float dot = d0 + d1;
+#pragma unroll
+                for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                u = bc * (vc - dot);
             }
-            float dot = d0 + d1;
-#pragma unroll
-            for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = plain ? vc : bc * (vc - dot);
             d0 = d1 = 0.f;
 #pragma unroll
             for (int i = 0; i < DL / 2; ++i) {
@@ -929,8 +936,15 @@ static int launch_delta_rule_split(const T* qkv, int ld, const T* b_in, int ldb,
                                    float q_scale, float* state, size_t state_stride, T* out, int ldo, float* o_raw,
                                    const int* row_slot, const int* row_last, const int* seg_row0, int segments, int n,
                                    int H, int G, int v_dim, int decay_mode, int gate_act, cudaStream_t stream) {
-    tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS>, dim3(H, v_dim / COLS, seg_row0 != nullptr ? segments : n), dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in, lda, A_log,
-               dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim, decay_mode);
+    const dim3 grid(H, v_dim / COLS, seg_row0 != nullptr ? segments : n);
+    if (decay_mode == DECAY_CONSTANT)
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, true>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+                   lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
+                   decay_mode);
+    else
+        tis_launch(delta_rule_split_kernel<T, DL, LANES, COLS, false>, grid, dim3(COLS * LANES), 0, stream, qkv, ld, b_in, ldb, a_in,
+                   lda, A_log, dt_bias, unit_eps, q_scale, state, state_stride, o_raw, row_slot, row_last, seg_row0, H, G, v_dim,
+                   decay_mode);
     int st = tis_check_launch("delta_rule");
     if (st != TIS_OK) return st;
     if (decay_mode == DECAY_CONSTANT) {
