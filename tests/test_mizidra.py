@@ -649,9 +649,11 @@ def test_router_and_experts(dtype, E, top, groups, shared):
 
 
 @gpu
-@pytest.mark.parametrize("n,d,F,E,top", [(300, 64, 96, 6, 3), (40, 96, 32, 16, 3), (1000, 32, 160, 3, 1), (129, 128, 64, 8, 8)])
+@pytest.mark.parametrize("n,d,F,E,top", [(300, 64, 96, 6, 3), (40, 96, 32, 16, 3), (1000, 32, 160, 3, 1), (129, 128, 64, 8, 8),
+                                         (700, 128, 192, 6, 3), (400, 64, 64, 16, 3), (1024, 256, 128, 4, 2), (2048, 320, 448, 16, 1)])
 def test_experts_of_many_rows(n, d, F, E, top):
-    """Many bfloat16 rows: sorted by expert on the device, tiles on the tensor cores.  Experts that no row chose, experts
+    """Many bfloat16 rows: sorted by expert on the device, tiles on the tensor cores (``mma.sync`` tiles of 64 rows; from
+    1024 pairs, with widths that are multiples of 64, ``tcgen05`` tiles of 128 rows).  Experts that no row chose, experts
     whose rows end in the middle of a tile, hidden sizes that end in the middle of a tile of columns; beside the kernels
     that take the same rows one dot product at a time."""
     from tiny_inference_server_b200.kernels import ops
@@ -672,9 +674,11 @@ def test_experts_of_many_rows(n, d, F, E, top):
     cdt = lambda t: t.to(torch.bfloat16).cuda().contiguous()
     w_gu = cdt(torch.stack([torch.stack([W[f"{p}e{e}.gate"], W[f"{p}e{e}.up"]]) for e in range(E)]))
     w_dn = cdt(torch.stack([W[f"{p}e{e}.down"] for e in range(E)]))
-    before = ops.calls["moe_grouped"]
+    before = ops.calls["moe_grouped"], ops.calls["moe_grouped_tc"]
     out = ops.moe_experts(x.cuda(), chosen.cuda(), weights.cuda(), w_gu, w_dn, extra.cuda(), sgate.cuda())
-    assert ops.calls["moe_grouped"] == before + 1
+    big = n * top >= 1024 and d % 64 == 0 and F % 64 == 0
+    assert (ops.calls["moe_grouped"], ops.calls["moe_grouped_tc"]) == (before[0] + (not big), before[1] + big)
+    assert int(ops.tc_fault()[0]) == 0
     one_by_one = ops.moe_down(ops.moe_gate_up(x.cuda(), chosen.cuda(), w_gu), chosen.cuda(), weights.cuda(), w_dn, extra.cuda(),
                               sgate.cuda())
     ref = sgate.double()[:, None] * extra.double()

@@ -316,11 +316,11 @@ namespace {
 
 constexpr int GT_ROWS = 64, GT_COLS = 64, GT_BK = 32, GT_STAGES = 3, GT_LD = GT_BK + 8;
 
-// One CTA.  counts -> every expert's first sorted row (a multiple of 64) -> tile_expert; then every pair (token,
+// One CTA.  counts -> every expert's first sorted row (a multiple of tile_rows) -> tile_expert; then every pair (token,
 // choice) takes the next free place of its expert: sorted_pair[place] = pair, pair_place[pair] = place.  Places that no
 // pair takes hold -1.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ chosen, int pairs, int E, int* __restrict__ sorted_pair, int max_rows,
+moe_sort_kernel(const int* __restrict__ chosen, int pairs, int E, int tile_rows, int* __restrict__ sorted_pair, int max_rows,
                 int* __restrict__ pair_place, int* __restrict__ tile_expert, int max_tiles) {
     extern __shared__ int sh[];
     int* counts = sh;              // [E]
@@ -339,8 +339,8 @@ moe_sort_kernel(const int* __restrict__ chosen, int pairs, int E, int* __restric
     if (tid == 0) {
         int tile = 0;
         for (int e = 0; e < E; ++e) {
-            starts[e] = tile * GT_ROWS;
-            const int tiles = (counts[e] + GT_ROWS - 1) / GT_ROWS;
+            starts[e] = tile * tile_rows;
+            const int tiles = (counts[e] + tile_rows - 1) / tile_rows;
             for (int t = 0; t < tiles && tile < max_tiles; ++t) tile_expert[tile++] = e;
         }
         for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
@@ -510,6 +510,21 @@ moe_combine_kernel(const bf16* __restrict__ y, int ldy, const int* __restrict__ 
 
 }  // namespace
 
+// The sort and the weighted sum, for the tile kernels of this file and of moe_tc.cu.
+int tis_moe_sort_launch(const int* chosen, int pairs, int E, int tile_rows, int* sorted_pair, int max_rows, int* pair_place,
+                        int* tile_expert, int max_tiles, cudaStream_t stream) {
+    tis_launch(moe_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * (size_t)E, stream, chosen, pairs, E, tile_rows,
+               sorted_pair, max_rows, pair_place, tile_expert, max_tiles);
+    return tis_check_launch("moe_sort");
+}
+
+int tis_moe_combine_launch(const void* y, int ldy, const int* pair_place, const float* weights, const void* shared, int lds,
+                           const float* shared_gate, void* out, int n, int d, int top, cudaStream_t stream) {
+    tis_launch(moe_combine_kernel, dim3(n), dim3(256), 0, stream, (const bf16*)y, ldy, pair_place, weights, (const bf16*)shared,
+               lds, shared_gate, (bf16*)out, d, top);
+    return tis_check_launch("moe_combine");
+}
+
 // Tiles of 64 sorted rows that `pairs` (token, choice) pairs over E experts can need at most.
 TIS_API int tis_moe_grouped_tiles(int pairs, int E) { return (pairs + GT_ROWS - 1) / GT_ROWS + E; }
 
@@ -529,9 +544,7 @@ TIS_API int tis_moe_grouped(const void* x, int ldx, const int* chosen, const flo
         return TIS_BAD_SIZE;
     }
     const int pairs = n * top, tiles = tis_moe_grouped_tiles(pairs, E);
-    tis_launch(moe_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * (size_t)E, stream, chosen, pairs, E, sorted_pair,
-               tiles * GT_ROWS, pair_place, tile_expert, tiles);
-    int st = tis_check_launch("moe_sort");
+    int st = tis_moe_sort_launch(chosen, pairs, E, GT_ROWS, sorted_pair, tiles * GT_ROWS, pair_place, tile_expert, tiles, stream);
     if (st != TIS_OK) return st;
     tis_launch(moe_grouped_kernel<true, true>, dim3(tiles, (F + GT_COLS - 1) / GT_COLS), dim3(128), 0, stream, (const bf16*)x,
                ldx, (const int*)sorted_pair, top, (const int*)tile_expert, (const bf16*)w_gu, (size_t)2 * F * d, (bf16*)hidden, F,
@@ -543,7 +556,5 @@ TIS_API int tis_moe_grouped(const void* x, int ldx, const int* chosen, const flo
                (bf16*)y, d, d, F);
     st = tis_check_launch("moe_grouped_down");
     if (st != TIS_OK) return st;
-    tis_launch(moe_combine_kernel, dim3(n), dim3(256), 0, stream, (const bf16*)y, d, (const int*)pair_place, weights,
-               (const bf16*)shared, lds, shared_gate, (bf16*)out, d, top);
-    return tis_check_launch("moe_combine");
+    return tis_moe_combine_launch(y, d, pair_place, weights, shared, lds, shared_gate, out, n, d, top, stream);
 }

@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 8
+ABI_VERSION = 9
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -1131,6 +1131,9 @@ def bitmap_set(bitmap_row: torch.Tensor, tokens: torch.Tensor) -> None:
 #: (token, choice) pairs from which bfloat16 expert products go to the tiles on the tensor cores (rows sorted by expert on
 #: the device) instead of one dot product per output element; TIS_MOE_GROUPED_MIN_PAIRS overrides (0: never)
 MOE_GROUPED_MIN_PAIRS = int(os.environ.get("TIS_MOE_GROUPED_MIN_PAIRS", "96"))
+#: pairs from which they go to the tcgen05 kernel (tiles of 128 rows, TMA-fed, accumulator in tensor memory) where width and
+#: hidden size are multiples of 64; TIS_MOE_TC_MIN_PAIRS overrides (0: never)
+MOE_TC_MIN_PAIRS = int(os.environ.get("TIS_MOE_TC_MIN_PAIRS", "1024"))
 
 
 def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
@@ -1143,9 +1146,29 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_
     n, d = x.shape
     top = chosen.shape[1]
     experts, _, hidden, _ = w_gate_up.shape
-    if (x.dtype == torch.bfloat16 and MOE_GROUPED_MIN_PAIRS > 0 and n * top >= MOE_GROUPED_MIN_PAIRS and d % 32 == 0
-            and hidden % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and (shared is None or (shared.stride(1) == 1 and shared.stride(0) % 2 == 0))):
+    grouped = (x.dtype == torch.bfloat16 and MOE_GROUPED_MIN_PAIRS > 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+               and x.data_ptr() % 16 == 0 and (shared is None or (shared.stride(1) == 1 and shared.stride(0) % 2 == 0)))
+    if grouped and MOE_TC_MIN_PAIRS > 0 and n * top >= MOE_TC_MIN_PAIRS and d % 64 == 0 and hidden % 64 == 0:
+        # many rows: 128-row tiles on the tcgen05 tensor cores, the stacked weights as TMA boxes where they lie
+        lib = library()
+        tiles = lib.tis_moe_tc_tiles(n * top, experts)
+        dev = x.device
+        meta = torch.empty(tiles * 128 + n * top + tiles, dtype=torch.int32, device=dev)
+        sorted_pair, pair_place, tile_expert = meta[:tiles * 128], meta[tiles * 128:tiles * 128 + n * top], meta[tiles * 128 + n * top:]
+        xs = torch.empty((tiles * 128, d), dtype=x.dtype, device=dev)
+        hid = torch.empty((tiles * 128, hidden), dtype=x.dtype, device=dev)
+        y = torch.empty((tiles * 128, d), dtype=x.dtype, device=dev)
+        out = torch.empty((n, d), dtype=x.dtype, device=dev)
+        calls["moe_grouped_tc"] += 1
+        global launches
+        launches += 4
+        _check(lib.tis_moe_grouped_tc(_p(x), x.stride(0), _p(chosen), _p(weights), _p(w_gate_up), _p(w_down), _p(shared),
+                                      shared.stride(0) if shared is not None else 0, _p(shared_gate), _p(out), _p(sorted_pair),
+                                      _p(pair_place), _p(tile_expert), _p(xs), _p(hid), _p(y), n, d, top, experts, hidden,
+                                      _p(tc_fault()), _stream()), lib)
+        return out
+    if (grouped and n * top >= MOE_GROUPED_MIN_PAIRS and d % 32 == 0
+            and hidden % 32 == 0):
         lib = library()
         tiles = lib.tis_moe_grouped_tiles(n * top, experts)
         dev = x.device
@@ -1155,7 +1178,6 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_
         y = torch.empty((tiles * 64, d), dtype=x.dtype, device=dev)
         out = torch.empty((n, d), dtype=x.dtype, device=dev)
         calls["moe_grouped"] += 1
-        global launches
         launches += 3
         _check(lib.tis_moe_grouped(_p(x), x.stride(0), _p(chosen), _p(weights), _p(w_gate_up), _p(w_down), _p(shared),
                                    shared.stride(0) if shared is not None else 0, _p(shared_gate), _p(out), _p(sorted_pair),
